@@ -1,0 +1,145 @@
+/*
+ * libternaspmm.so - C ABI of the TernaSpMM operator for NVIDIA B200 (sm_100a).
+ *
+ * TernaSpMM is a linear layer  out[M,N] = x_q[M,K] * W[N,K]^T  with ternary
+ * weights W in {-1,0,+1} stored compressed (1-bit non-zero bitmaps + packed
+ * sign bits of the non-zeros + per-tile offsets), int8 activations x_q with a
+ * per-token bf16 scale s, a 4-slot bf16 per-segment weight scale ws, and bf16
+ * output.  The entry points, their argument order and their meaning are those
+ * of the reference library (citations: file:line inside Gu-J/TernaInfer), so a
+ * caller that binds the reference's libternaspmm.so binds this one unchanged.
+ *
+ * Plain C: pointers and sizes only.  bf16 values are passed as uint16_t bit
+ * patterns; a CUDA stream is passed as an opaque pointer (cudaStream_t).
+ *
+ * Ownership: the caller owns every device buffer; the compute entry points
+ * allocate nothing, never synchronise and never copy through the host, so
+ * they may be called while the stream is being captured into a CUDA graph.
+ *
+ * Weight layout: the four arrays keep the reference's element types and
+ * sizes (bitmap N*K/64 u64, tile_offsets N*K/4096+1 i32, quarter_offsets
+ * 3*N*K/4096 u16, sign_words tile_offsets[last]/32 u32) but the order of the
+ * 4096 weights inside a 64x64 tile is the B200 order produced by
+ * convert_reorderd() / the Python packer, not the reference's mma.m16n8k16
+ * order.  ternaspmm_transcode_reference_layout() converts arrays packed by the
+ * reference's packer.  Requirements: N % 64 == 0, K % 64 == 0, M >= 1,
+ * x / bitmap / sign_words 16-byte aligned, sign_words readable up to the next
+ * 16-byte boundary after its last word.
+ */
+#ifndef TERNASPMM_H_
+#define TERNASPMM_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* ternaspmm_stream_t; /* cudaStream_t */
+typedef uint16_t ternaspmm_bf16;  /* bf16 bit pattern */
+
+/* ---- entry points that replace the reference's, same signatures -------- */
+
+/* Replaces bitlinear_TernaSpMM (kernels/TernaSpMM.cu:25-71).  M <= 64 uses
+ * the decode epilogue  bf16(float(acc)/s[t]*ws[g]), M > 64 the prefill
+ * epilogue  bf16(float(acc)*(ws[g]/s[t])).  split_k and workspace are
+ * accepted for compatibility; the K-split is chosen internally and reduced
+ * through cluster shared memory, the workspace is never touched. */
+void bitlinear_TernaSpMM(int8_t* x, uint64_t* bitmap, int* tile_offsets,
+                         uint16_t* quarter_offsets, uint32_t* sign_words,
+                         ternaspmm_bf16* out, ternaspmm_bf16* s, ternaspmm_bf16* ws,
+                         int ws_num, int M, int N, int K, int split_k,
+                         int32_t* workspace, ternaspmm_stream_t stream);
+
+/* Replaces bitlinear_TernaSpMM_decode (kernels/TernaSpMM.cu:79-107): decode
+ * epilogue for any M. */
+void bitlinear_TernaSpMM_decode(int8_t* x, uint64_t* bitmap, int* tile_offsets,
+                                uint16_t* quarter_offsets, uint32_t* sign_words,
+                                ternaspmm_bf16* out, ternaspmm_bf16* s, ternaspmm_bf16* ws,
+                                int ws_num, int M, int N, int K, int split_k,
+                                int32_t* workspace, ternaspmm_stream_t stream);
+
+/* Replaces bitlinear_TernaSpMM_prefill (kernels/TernaSpMM.cu:110-138):
+ * prefill epilogue for any M. */
+void bitlinear_TernaSpMM_prefill(int8_t* x, uint64_t* bitmap, int* tile_offsets,
+                                 uint16_t* quarter_offsets, uint32_t* sign_words,
+                                 ternaspmm_bf16* out, ternaspmm_bf16* s, ternaspmm_bf16* ws,
+                                 int ws_num, int M, int N, int K, int split_k,
+                                 int32_t* workspace, ternaspmm_stream_t stream);
+
+/* Replaces bitlinear_TernaSpMM_benchmark (kernels/TernaSpMM.cu:141-236):
+ * mode 0/1/2 = auto/prefill/decode (out of range -> 0); warm-up, CUDA-event
+ * timing loop, prints "Shape(M=.., N=.., K=..): %.2f us ...".  Synchronises. */
+void bitlinear_TernaSpMM_benchmark(int mode, int warmup_iters, int bench_iters,
+                                   int8_t* x, uint64_t* bitmap, int* tile_offsets,
+                                   uint16_t* quarter_offsets, uint32_t* sign_words,
+                                   ternaspmm_bf16* out, ternaspmm_bf16* s, ternaspmm_bf16* ws,
+                                   int ws_num, int M, int N, int K, int split_k,
+                                   int32_t* workspace, ternaspmm_stream_t stream);
+
+/* Replaces checkLastCudaError (kernels/TernaSpMM.cu:15-22): prints and
+ * exit(EXIT_FAILURE) when cudaGetLastError() reports an error. */
+void checkLastCudaError(int line);
+
+/* Replaces reorder_WT_h (kernels/TernaSpMM.cu:241-280).  Host buffers, bf16
+ * [N][K].  The B200 layout needs no pre-permutation, so this is a copy; it is
+ * kept so that callers written against the reference (tests/test_kernel.cu:
+ * 253) keep working. */
+void reorder_WT_h(ternaspmm_bf16* W, ternaspmm_bf16* W_reordered, int N, int K);
+
+/* Replaces convert_reorderd (kernels/TernaSpMM.cu:282-439): host packer.
+ * Input bf16 [N][K] holding {-1,0,+1}.  The six tile arguments must be
+ * 64,16,8,64,64,8 as in the reference's only call (tests/test_kernel.cu:255).
+ * Allocates the outputs like the reference: tile_offsets, quarter_offsets and
+ * sign_words with malloc (caller frees), bitmap with cudaMallocHost (caller
+ * cudaFreeHost).  *max_nnz receives the largest padded per-tile count (the
+ * reference declares this parameter as int&, the same ABI).  Returns the
+ * number of 64x64 tiles or -1. */
+int convert_reorderd(ternaspmm_bf16* W, int N, int K, int tile_N, int warp_subtile_N,
+                     int subtile_N, int tile_K, int warp_subtile_K, int subtile_K,
+                     uint64_t** bitmap, int** tile_offsets, uint16_t** quarter_offsets,
+                     uint32_t** sign_words, int* max_nnz);
+
+/* Replaces gpu_sleep (kernels/TernaSpMM.cu:442-457): a one-warp spacer kernel
+ * that waits sleep_us microseconds (bounded at one second). */
+void gpu_sleep(double sleep_us, ternaspmm_stream_t stream);
+
+/* ---- additions (no counterpart in the reference) ------------------------ */
+
+/* Status of the most recent compute call on this thread's device: 0 = ok,
+ * 1 = bad shape, 2 = bad pointer/alignment, 3 = launch failure, 4 = a device
+ * wait on a bulk copy ran out (kernel returned early).  Reading the device
+ * word synchronises the device; do not call while capturing. */
+int ternaspmm_last_status(void);
+
+/* Test hook: same contraction, raw int32 accumulators out[M][N]. */
+void ternaspmm_accumulate_i32(int8_t* x, uint64_t* bitmap, int* tile_offsets,
+                              uint16_t* quarter_offsets, uint32_t* sign_words,
+                              int32_t* out, int M, int N, int K,
+                              ternaspmm_stream_t stream);
+
+/* Host packer from int8 ternary [N][K] into caller-provided arrays
+ * (bitmap N*K/64, tile_offsets tiles+1, quarter_offsets 3*tiles, sign_words
+ * at least N*K/32 + 4 words, zero-filled by the call).  Returns the number of
+ * sign words used, or -1. */
+long long ternaspmm_pack_i8(const int8_t* W, int N, int K, uint64_t* bitmap,
+                            int* tile_offsets, uint16_t* quarter_offsets,
+                            uint32_t* sign_words);
+
+/* Inverse of the packer (host): writes int8 ternary [N][K]. Returns 0/-1. */
+int ternaspmm_unpack_i8(const uint64_t* bitmap, const int* tile_offsets,
+                        const uint32_t* sign_words, int N, int K, int8_t* W);
+
+/* Host transcoder: arrays packed by the reference's compress_weight
+ * (convert/convert_utils.py:52-228) -> B200 layout.  tile_offsets are the
+ * same in both layouts; bitmap, sign_words and the three per-tile u16 are
+ * rewritten into the out_* arrays (same sizes as the inputs). */
+int ternaspmm_transcode_reference_layout(const uint64_t* ref_bitmap, const int* tile_offsets,
+                                         const uint32_t* ref_sign_words, int N, int K,
+                                         uint64_t* out_bitmap, uint16_t* out_quarter_offsets,
+                                         uint32_t* out_sign_words);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TERNASPMM_H_ */

@@ -1,0 +1,116 @@
+"""Call site of the TernaSpMM operator: the PyTorch side of the boundary.
+
+Mirrors ``TernaInfer_linear`` / ``SpBitLinear`` / ``get_global_workspace`` of
+the reference's ``model.py`` (:37-133 in Gu-J/TernaInfer): same names, same
+argument meaning, same checkpoint keys.  Differences, all on this side of the
+C ABI: the activation quantiser runs as plain torch ops (no ``torch.compile``,
+hence no Triton); rows are not padded to a power of two because the B200
+library accepts any token count >= 1; the workspace is accepted and ignored
+(the library reduces its K split on chip).
+
+PyTorch is only plumbing here (device memory, the current stream); all
+arithmetic of the linear layer happens in ``libternaspmm.so``.  There is no
+CPU path: calling with CPU tensors raises.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+from torch import nn
+
+from .lib import load_library
+
+_GLOBAL_WORKSPACE = None
+
+
+def get_global_workspace(device="cuda"):
+    """Kept for drop-in compatibility (model.py:37-42).  The B200 kernels do
+    not use a workspace, so a 16-byte placeholder is returned."""
+    global _GLOBAL_WORKSPACE
+    if _GLOBAL_WORKSPACE is None:
+        _GLOBAL_WORKSPACE = torch.empty(16, dtype=torch.int8, device=device)
+    return _GLOBAL_WORKSPACE
+
+
+def quant_input(input: torch.Tensor):
+    """Per-token absmax int8 quantisation (model.py:120-123):
+    s = 127 / clamp(max|x|, 1e-5); x_q = clamp(round(x*s), -128, 127)."""
+    s = 127 / input.abs().max(dim=-1, keepdim=True).values.clamp_(min=1e-5)
+    return (input * s).round().clamp(-128, 127).to(torch.int8), s
+
+
+_ENTRY = {"auto": "bitlinear_TernaSpMM", "decode": "bitlinear_TernaSpMM_decode",
+          "prefill": "bitlinear_TernaSpMM_prefill"}
+
+
+def TernaInfer_linear(input, compressed_val, TileOffsets_global, TileOffsets_median, bitmap,
+                      workspace, s, ws, ws_num, out_features, mode: str = "auto"):
+    """out = TernaSpMM(input_int8, packed weight) as bf16 (model.py:45-92).
+    ``input`` is int8 [..., K] on the GPU, ``s`` its per-token bf16 scale,
+    ``ws`` the 4-slot bf16 weight scale with ``ws_num`` non-zero slots."""
+    if not input.is_cuda:
+        raise RuntimeError("TernaInfer_linear needs CUDA tensors: the B200 library has no CPU path")
+    lib = load_library()
+    out_shape = list(input.shape)
+    out_shape[-1] = out_features
+    K = input.shape[-1]
+    M = input.numel() // K
+    x2 = input.reshape(M, K)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    if s.dtype != torch.bfloat16:
+        s = s.to(torch.bfloat16)
+    s = s.contiguous()
+    ret = torch.empty((M, out_features), dtype=torch.bfloat16, device=input.device)
+    stream = torch.cuda.current_stream()
+    getattr(lib, _ENTRY[mode])(
+        ctypes.c_void_p(x2.data_ptr()),
+        ctypes.c_void_p(bitmap.data_ptr()),
+        ctypes.c_void_p(TileOffsets_global.data_ptr()),
+        ctypes.c_void_p(TileOffsets_median.data_ptr()),
+        ctypes.c_void_p(compressed_val.data_ptr()),
+        ctypes.c_void_p(ret.data_ptr()),
+        ctypes.c_void_p(s.data_ptr()),
+        ctypes.c_void_p(ws.data_ptr()),
+        ctypes.c_int(ws_num),
+        ctypes.c_int(M), ctypes.c_int(out_features), ctypes.c_int(K),
+        ctypes.c_int(1), ctypes.c_void_p(workspace.data_ptr() if workspace is not None else 0),
+        ctypes.c_void_p(stream.cuda_stream),
+    )
+    return ret.reshape(*out_shape)
+
+
+class SpBitLinear(nn.Module):
+    """Ternary linear layer bound to packed checkpoint tensors (model.py:96-133):
+    ``<key>.weight_compressed_val`` (uint32), ``_TileOffsets_global`` (int32),
+    ``_TileOffsets_median`` (uint16), ``_bitmap`` (uint64), ``.weight_scale``
+    (bf16[4])."""
+
+    def __init__(self, in_features: int, out_features: int, dic: dict, key: str, bias: bool = False):
+        super().__init__()
+        self.in_features = in_features
+        self.out_features = out_features
+        dev = "cuda"
+        self.weight_compressed_val = nn.Parameter(dic[key + ".weight_compressed_val"].to(dev), requires_grad=False)
+        self.weight_TileOffsets_global = nn.Parameter(dic[key + ".weight_TileOffsets_global"].to(dev),
+                                                      requires_grad=False)
+        self.weight_TileOffsets_median = nn.Parameter(dic[key + ".weight_TileOffsets_median"].to(dev),
+                                                      requires_grad=False)
+        self.weight_bitmap = nn.Parameter(dic[key + ".weight_bitmap"].to(dev), requires_grad=False)
+        ws = dic[key + ".weight_scale"]
+        self.weight_scale = nn.Parameter(ws.to(dev), requires_grad=False)
+        self.ws_num = int((ws != 0).sum().item())
+
+    quant_input = staticmethod(quant_input)
+
+    def forward(self, input):
+        input, s = quant_input(input)
+        return TernaInfer_linear(
+            input,
+            self.weight_compressed_val, self.weight_TileOffsets_global, self.weight_TileOffsets_median,
+            self.weight_bitmap,
+            get_global_workspace(input.device),
+            s, self.weight_scale, self.ws_num,
+            self.out_features,
+        )
