@@ -1,0 +1,379 @@
+#!/usr/bin/env python
+"""Benchmark of the TernaSpMM hot path on B200.
+
+Workload (BASELINE.json configs[1], the linear-layer sweep): the four ternary
+linears of a BitNet-b1.58-2B decoder layer - QKV 2560->3840 (3 scale segments),
+O 2560->2560, gate-up 2560->13824 (2 segments), down 6912->2560 - for
+``--layers`` layers with distinct random weights (30 layers = 410 MB of
+compressed weights, more than three times the L2, so every call streams its
+weights from HBM) at ``--tokens`` tokens.  One step = one pass over all
+4 * layers linears.  Synthetic seeded inputs: weights i.i.d. over {-1,0,+1}
+with P(0)=0.45, activations N(0,1) quantised per token to int8.
+
+Prints ONE JSON line.  ``value`` = algorithmic bytes (compressed weights +
+activations + scales + bf16 outputs) of all ranks per second with every input
+resident in HBM, the step replayed as a CUDA graph; ``e2e`` = the same metric
+through the Python call site (``TernaInfer_linear``) with the activations
+copied from pinned host memory and the outputs copied back every step.
+``--impl reference`` times the CPU restatement of the reference's arithmetic
+(the reference has no CPU implementation of this path and its CUDA library
+does not build without an un-vendored CUTLASS) on the host cores.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np
+
+SHAPES = [  # name, N, K, ws_num
+    ("wqkv", 3840, 2560, 3),
+    ("wo", 2560, 2560, 1),
+    ("w13", 13824, 2560, 2),
+    ("w2", 2560, 6912, 1),
+]
+P_ZERO = 0.45
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed
+    region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ----------------------------------------------------------------------------
+# CPU arm: the oracle port timed on the host cores (checker code, used here
+# only as the thing to compare against, never on the GPU arm's path).
+# ----------------------------------------------------------------------------
+
+def cpu_sample(tokens, seconds_budget, seed=1234):
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import ternaspmm_oracle as o
+    import c_oracle
+    lib = c_oracle.load()
+    cores = int(lib.oracle_num_threads())
+    items, alg = [], 0
+    for li, (name, N, K, ws_num) in enumerate(SHAPES):
+        rng = np.random.default_rng(seed + li)
+        w = (rng.random((N, K), dtype=np.float32) >= P_ZERO).astype(np.int8)
+        w *= (rng.integers(0, 2, size=(N, K), dtype=np.int8) * 2 - 1)
+        xq, s = o.make_activations(tokens, K, seed + 100 + li)
+        ws = o.make_ws(ws_num, seed + 200 + li)
+        nnz = int(np.count_nonzero(w))
+        tiles = N * K // 4096
+        wbytes = N * K // 8 + (nnz + 16 * tiles) // 8 + 4 * (tiles + 1) + 6 * tiles   # padding estimated at 16 bits/tile
+        alg += wbytes + tokens * K + 2 * tokens + 8 + 2 * tokens * N
+        items.append((xq, w, o.f32_to_bf16_bits(s.reshape(-1)), o.f32_to_bf16_bits(ws), ws_num))
+    def one_pass():
+        for xq, w, sb, wb, ws_num in items:
+            c_oracle.ternaspmm(xq, w, sb, wb, ws_num)
+    one_pass()
+    t0 = time.perf_counter()
+    one_pass()
+    dt = time.perf_counter() - t0
+    reps = max(1, min(200, int(seconds_budget / max(dt, 1e-6))))
+    return one_pass, alg, cores, reps, dt
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    one_pass, alg, cores, reps, _ = cpu_sample(args.tokens, 2.0)
+    for _ in range(args.warmup):
+        one_pass()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for _ in range(reps):
+            one_pass()
+    dt = time.perf_counter() - t0
+    val = alg * reps * args.steps / dt / 1e9
+    sample = f"{reps} passes over one layer (4 linears) per step at {args.tokens} tokens, dense ternary int8 weights"
+    line = {
+        "impl": "reference", "metric": "ternaspmm_algorithmic_GBps", "value": val, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8xternary->int32->bf16",
+        "data": "synthetic",
+        "config": {"workload": f"bitnet2b_linear_sweep_M{args.tokens}", "tokens": args.tokens, "p_zero": P_ZERO,
+                   "note": "CPU restatement of the reference arithmetic (C, OpenMP); the reference has no CPU path"},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------
+
+def build_workload(torch, layers, tokens, seed, device):
+    from ternainfer_b200.convert import compress_weight, compressed_nbytes
+    gen = torch.Generator(device=device)
+    work, wbytes_total = [], 0
+    for layer in range(layers):
+        for si, (name, N, K, ws_num) in enumerate(SHAPES):
+            gen.manual_seed(seed + 1000 * layer + si)
+            r = torch.rand((N, K), generator=gen, device=device)
+            sign = (torch.randint(0, 2, (N, K), generator=gen, device=device, dtype=torch.int8) * 2 - 1)
+            w = torch.where(r < P_ZERO, torch.zeros((), dtype=torch.int8, device=device), sign)
+            cv, tg, tm, bm = compress_weight(w)
+            nbytes = compressed_nbytes(cv, tg, tm, bm)
+            ws = torch.zeros(4, device=device)
+            ws[:ws_num] = torch.rand(ws_num, generator=gen, device=device) * 0.04 + 0.01
+            item = dict(name=name, N=N, K=K, ws_num=ws_num, cv=cv, tg=tg, tm=tm, bm=bm, ws=ws.to(torch.bfloat16),
+                        wbytes=nbytes, alg=nbytes + tokens * K + 2 * tokens + 8 + 2 * tokens * N)
+            if layer == 0:
+                item["dense"] = w.cpu().numpy()
+            work.append(item)
+            wbytes_total += nbytes
+            del w, r, sign
+    return work, wbytes_total
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+    from ternainfer_b200 import load_library
+    from ternainfer_b200.linear import TernaInfer_linear, quant_input
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA GPU: the TernaSpMM library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    lib = load_library()   # raises if the CUDA library is missing
+    M = args.tokens
+
+    work, wbytes_total = build_workload(torch, args.layers, M, args.seed + 7919 * rank, device)
+    alg_step = sum(it["alg"] for it in work)
+
+    # activations: one bf16 matrix per input width, quantised once (resident leg)
+    gen = torch.Generator(device="cpu").manual_seed(args.seed + 5)
+    x_host = {K: torch.randn((M, K), generator=gen).to(torch.bfloat16).pin_memory() for K in (2560, 6912)}
+    xq, s = {}, {}
+    for K, xh in x_host.items():
+        xq[K], s[K] = quant_input(xh.to(device))
+        s[K] = s[K].contiguous()
+    xq_host = {K: v.cpu().pin_memory() for K, v in xq.items()}
+    s_host = {K: v.cpu().pin_memory() for K, v in s.items()}
+    outs = [torch.empty((M, it["N"]), dtype=torch.bfloat16, device=device) for it in work]
+    stream = torch.cuda.Stream(device=device)
+
+    def launch_all():
+        st = torch.cuda.current_stream().cuda_stream
+        for it, out in zip(work, outs):
+            K = it["K"]
+            lib.bitlinear_TernaSpMM(xq[K].data_ptr(), it["bm"].data_ptr(), it["tg"].data_ptr(), it["tm"].data_ptr(),
+                                    it["cv"].data_ptr(), out.data_ptr(), s[K].data_ptr(), it["ws"].data_ptr(),
+                                    it["ws_num"], M, it["N"], K, 7, 0, st)
+
+    # sanity (outside the timed region): layer 0 against the CPU oracle
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import ternaspmm_oracle as o
+    with torch.cuda.stream(stream):
+        launch_all()
+    stream.synchronize()
+    for it, out in zip(work[:len(SHAPES)], outs[:len(SHAPES)]):
+        K = it["K"]
+        want = o.ternaspmm(xq[K].cpu().numpy(), it["dense"], s[K].float().cpu().numpy().reshape(-1),
+                           it["ws"].float().cpu().numpy(), it["ws_num"])
+        got = out.view(torch.int16).cpu().numpy().view(np.uint16)
+        if not (got == want).all():
+            raise SystemExit(f"bench sanity check failed for {it['name']}: GPU result differs from the oracle")
+    if lib.ternaspmm_last_status() != 0:
+        raise SystemExit("bench: library reported a non-zero status")
+
+    # resident leg: the whole step as one CUDA graph
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            launch_all()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            graph.replay()
+        barrier()
+        if rank == 0:
+            sampler.start()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        ev1.record(stream)
+        barrier()
+    ms = ev0.elapsed_time(ev1)
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+
+    # end-to-end leg: Python call site, host buffers in and out every step
+    out_host = [torch.empty((M, it["N"]), dtype=torch.bfloat16).pin_memory() for it in work]
+    xq_dev = {K: torch.empty_like(v, device=device) for K, v in xq_host.items()}
+    s_dev = {K: torch.empty_like(v, device=device) for K, v in s_host.items()}
+    h2d = sum(v.numel() * v.element_size() for v in xq_host.values()) + \
+        sum(v.numel() * v.element_size() for v in s_host.values())
+    d2h = sum(v.numel() * v.element_size() for v in out_host)
+
+    def e2e_step():
+        for K in xq_host:
+            xq_dev[K].copy_(xq_host[K], non_blocking=True)
+            s_dev[K].copy_(s_host[K], non_blocking=True)
+        for it, oh in zip(work, out_host):
+            K = it["K"]
+            y = TernaInfer_linear(xq_dev[K], it["cv"], it["tg"], it["tm"], it["bm"], None, s_dev[K], it["ws"],
+                                  it["ws_num"], it["N"])
+            oh.copy_(y, non_blocking=True)
+
+    with torch.cuda.stream(stream):
+        for _ in range(max(3, args.warmup)):
+            e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            e2e_step()
+        e1.record(stream)
+        barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    t2 = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t2.item())
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        launches = len(work)
+        value = alg_step * world * args.steps / (ms_max * 1e-3) / 1e9
+        per_launch_us = ms_max * 1e3 / (args.steps * launches)
+        achieved = (alg_step / launches) / (per_launch_us * 1e-6) / 1e9
+        e2e_val = alg_step * world * args.steps / (e2e_ms * 1e-3) / 1e9
+        one_pass, cpu_alg, cores, reps, dt = cpu_sample(M, 3.0)
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            one_pass()
+        cpu_dt = time.perf_counter() - t0
+        line = {
+            "metric": "ternaspmm_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_max / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8xternary->int32->bf16", "data": "synthetic",
+            "config": {"workload": f"bitnet2b_linear_sweep_M{M}", "tokens": M, "layers": args.layers,
+                       "linears_per_step": launches, "p_zero": P_ZERO, "seed": args.seed,
+                       "compressed_weight_bytes_per_rank": wbytes_total,
+                       "l2_policy": "inputs larger than L2: each step streams %.0f MB of distinct weights" %
+                                    (wbytes_total / 1e6),
+                       "parallelism": "replicas only" if world > 1 else "single GPU",
+                       "launch": "one CUDA graph replay per step"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "peak_kind": "of " + peak_kind,
+                         "frac_of_nominal_8000": achieved / 8000.0,
+                         "kernel": "spmm_small_m_kernel", "avg_launch_us": per_launch_us,
+                         "algorithmic_bytes_per_launch": alg_step / launches, "traffic": None},
+            "cpu_baseline": {"value": cpu_alg * reps / cpu_dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+                             "sample": f"{reps} passes over one layer (4 linears) at {M} tokens, dense int8 ternary "
+                                       f"weights, {cpu_dt:.1f} s"},
+            "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms / args.steps, "api": "ternainfer_b200.linear.TernaInfer_linear"},
+            "gpu_launches": launches * args.steps,
+            "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=30)
+    ap.add_argument("--seed", type=int, default=1234)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -63,13 +63,45 @@ def _pack_tiles(t: np.ndarray):
     return words, tile_off.astype(np.int32), quarters, bitmap
 
 
+def _compress_weight_cuda(weight: torch.Tensor):
+    """Same packing with torch ops on the GPU (used for large models)."""
+    N, K = weight.shape
+    rt, kt = N // 64, K // 64
+    dev = weight.device
+    t = weight.reshape(rt, 4, 2, 8, kt, 4, 2, 2, 4).permute(0, 4, 3, 5, 1, 6, 7, 2, 8).reshape(rt * kt, 4096)
+    tiles = t.shape[0]
+    nz = t != 0
+    pow2 = torch.ones(32, dtype=torch.int64, device=dev) << torch.arange(32, dtype=torch.int64, device=dev)
+
+    def pack32(bits):  # [..., 32] bool -> uint32 words (as int32 bit patterns)
+        v = (bits.to(torch.int64) * pow2).sum(-1)
+        return torch.where(v >= 2 ** 31, v - 2 ** 32, v).to(torch.int32)
+
+    bm_words = pack32(nz.reshape(tiles, 128, 32)).reshape(-1)
+    csum = nz.cumsum(1, dtype=torch.int32)
+    cnt = csum[:, -1].to(torch.int64)
+    tile_off = torch.zeros(tiles + 1, dtype=torch.int64, device=dev)
+    tile_off[1:] = ((cnt + 31) // 32 * 32).cumsum(0)
+    quarters = csum[:, [1023, 2047, 3071]].to(torch.int16).reshape(-1)
+    total = int(tile_off[-1].item())
+    bits = torch.zeros(total + 32 * _PAD_WORDS, dtype=torch.bool, device=dev)
+    pos = (tile_off[:-1, None] + csum.to(torch.int64) - 1)[nz]
+    bits[pos] = (t < 0)[nz]
+    words = pack32(bits.reshape(-1, 32))
+    return (words.view(torch.uint32), tile_off.to(torch.int32), quarters.view(torch.uint16),
+            bm_words.reshape(-1, 2).contiguous().view(torch.int64).reshape(-1).view(torch.uint64))
+
+
 def compress_weight(weight: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """int8 ternary [N, K] (N, K multiples of 64) -> (compressed_val,
-    TileOffsets_global, TileOffsets_median, bitmap)."""
+    TileOffsets_global, TileOffsets_median, bitmap).  CPU tensors are packed
+    with numpy, CUDA tensors on the GPU; results stay on the input's device."""
     assert weight.dtype == torch.int8 and weight.dim() == 2
     N, K = weight.shape
     assert N % 64 == 0 and K % 64 == 0, "N and K must be multiples of 64"
-    w = weight.detach().cpu().contiguous().numpy()
+    if weight.is_cuda:
+        return _compress_weight_cuda(weight.detach().contiguous())
+    w = weight.detach().contiguous().numpy()
     words, tile_off, quarters, bitmap = _pack_tiles(_tile_view(w))
     return (torch.from_numpy(words.astype(np.uint32)), torch.from_numpy(tile_off),
             torch.from_numpy(quarters.copy()), torch.from_numpy(bitmap.astype(np.uint64)))

@@ -75,6 +75,10 @@ __device__ __forceinline__ void red_add_cluster(uint32_t cluster_addr, int v) {
     asm volatile("red.relaxed.cluster.shared::cluster.add.s32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 
+// ------------------------------------------- programmatic dependent launch
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ----------------------------------------------------- shared vector access
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;

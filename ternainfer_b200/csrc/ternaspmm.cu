@@ -44,47 +44,93 @@ static int device_sm_count() {
     return sms[dev];
 }
 
-template <int MT, int MAXW>
-static cudaError_t launch_small_m(const SpmmParams& p, int token_blocks, cudaStream_t stream) {
+// Launch-shape knobs, read once from the environment (for tuning runs):
+// TERNASPMM_CTAS_PER_SM_X10 (0 = automatic one-wave choice),
+// TERNASPMM_MAX_WARPS (cap on warps per CTA), TERNASPMM_PDL=0 to launch
+// without programmatic dependent launch.
+struct Tuning {
+    int ctas_x10 = 0, max_warps = 0, pdl = 1;
+    Tuning() {
+        if (const char* e = getenv("TERNASPMM_CTAS_PER_SM_X10")) ctas_x10 = atoi(e);
+        if (const char* e = getenv("TERNASPMM_MAX_WARPS")) max_warps = atoi(e);
+        if (const char* e = getenv("TERNASPMM_PDL")) pdl = atoi(e) != 0;
+    }
+};
+static const Tuning& tuning() {
+    static Tuning t;
+    return t;
+}
+
+struct LaunchShape {
+    int splits, warps;
+};
+
+// K split (= cluster size, at most 8) and warps per CTA.  Take the smallest
+// number of tiles per warp for which every CTA is resident at once (one wave:
+// `warp_slots` warps and at most 3 CTAs per SM at this kernel's register and
+// shared-memory budget), and for that the smallest cluster.
+// TERNASPMM_CTAS_PER_SM_X10 > 0 overrides with "about that many CTAs per SM".
+static LaunchShape choose_shape(int RT, int KT, int token_blocks, int max_warps, int warp_slots) {
+    const int sms = device_sm_count();
+    const long long rows = (long long)RT * token_blocks;
+    const int max_w = tuning().max_warps > 0 && tuning().max_warps < max_warps ? tuning().max_warps : max_warps;
+    const int max_s = KT > 1 ? (KT / 2 < 8 ? KT / 2 : 8) : 1;
+    if (tuning().ctas_x10 > 0) {
+        const long long target = (long long)tuning().ctas_x10 * sms / 10;
+        int s = (int)((target + rows - 1) / rows);
+        s = s > max_s ? max_s : (s < 1 ? 1 : s);
+        const int nt = (KT + s - 1) / s;
+        return {s, nt < 2 ? 2 : (nt > max_w ? max_w : nt)};
+    }
+    for (int tpw = 1; tpw <= KT; ++tpw)
+        for (int s = 1; s <= max_s; ++s) {
+            const int nt = (KT + s - 1) / s;
+            int w = (nt + tpw - 1) / tpw;
+            if (w > max_w) continue;
+            if (w < 2) w = 2;
+            int per_sm = warp_slots / w;
+            per_sm = per_sm > 3 ? 3 : per_sm;
+            if (rows * s <= (long long)sms * per_sm) return {s, w};
+        }
+    const int nt = (KT + max_s - 1) / max_s;   // more than one wave whatever we do
+    return {max_s, nt < 2 ? 2 : (nt > max_w ? max_w : nt)};
+}
+
+template <int MT, int MAXW, int MINB>
+static cudaError_t launch_small_m(SpmmParams& p, int token_blocks, int warp_slots, cudaStream_t stream) {
     using L = SmallMSmem<MT>;
     static bool attr_done[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
-    auto kern = spmm_small_m_kernel<MT, MAXW>;
+    auto kern = spmm_small_m_kernel<MT, MAXW, MINB>;
+    const LaunchShape shape = choose_shape(p.N / 64, p.K / 64, token_blocks, MAXW, warp_slots);
+    p.splits = shape.splits;
+    const int warps = shape.warps;
     if (!attr_done[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
         if (e != cudaSuccess) return e;
         attr_done[dev] = true;
     }
-    const int RT = p.N / 64, KT = p.K / 64;
-    const int nt = (KT + p.splits - 1) / p.splits;
-    int warps = nt < 2 ? 2 : (nt > MAXW ? MAXW : nt);
+    const int RT = p.N / 64;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.splits, RT, token_blocks);
     cfg.blockDim = dim3(warps * 32, 1, 1);
     cfg.dynamicSmemBytes = L::total;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = p.splits;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // Programmatic dependent launch: this kernel may start while the previous
+    // kernel of the stream still runs; it prefetches its (immutable) weights
+    // and waits (griddepcontrol.wait) before touching activations or outputs.
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = tuning().pdl ? 2 : 1;
     return cudaLaunchKernelEx(&cfg, kern, p);
-}
-
-// K split (= cluster size, at most 8): enough CTAs to fill the device about
-// twice, but never fewer than two k-tiles per CTA.
-static int choose_splits(int RT, int KT, int token_blocks) {
-    const int target = 2 * device_sm_count();
-    const long long ctas = (long long)RT * token_blocks;
-    int s = (int)((target + ctas - 1) / ctas);
-    if (s > 8) s = 8;
-    if (s > KT / 2) s = KT / 2;
-    if (s < 1) s = 1;
-    return s;
 }
 
 static void run_spmm(int8_t* x, uint64_t* bitmap, int* tile_off, uint16_t* quarter_off, uint32_t* signs, void* out,
@@ -126,15 +172,11 @@ static void run_spmm(int8_t* x, uint64_t* bitmap, int* tile_off, uint16_t* quart
     }
     cudaError_t e;
     if (M <= 8) {
-        p.splits = choose_splits(N / 64, K / 64, 1);
-        e = launch_small_m<1, 16>(p, 1, stream);
+        e = launch_small_m<1, 16, 2>(p, 1, 32, stream);
     } else if (M <= 16) {
-        p.splits = choose_splits(N / 64, K / 64, 1);
-        e = launch_small_m<2, 16>(p, 1, stream);
+        e = launch_small_m<2, 16, 1>(p, 1, 16, stream);
     } else {
-        const int tb = (M + 31) / 32;
-        p.splits = choose_splits(N / 64, K / 64, tb);
-        e = launch_small_m<4, 8>(p, tb, stream);
+        e = launch_small_m<4, 8, 2>(p, (M + 31) / 32, 16, stream);
     }
     if (e != cudaSuccess) {
         fprintf(stderr, "ternaspmm: launch failed: %s\n", cudaGetErrorString(e));
@@ -245,5 +287,13 @@ extern "C" void bitlinear_TernaSpMM_benchmark(int mode, int warmup_iters, int be
     cudaEventDestroy(start);
     cudaEventDestroy(stop);
 }
+
+#ifdef TSP_PHASE_TIMERS
+// Tuning builds only: copy the per-CTA phase timestamps of the last launch.
+extern "C" int ternaspmm_debug_read_phases(unsigned long long* dst, int ctas) {
+    if (ctas > 4096) ctas = 4096;
+    return (int)cudaMemcpyFromSymbol(dst, g_phase_log, sizeof(unsigned long long) * ctas * kPhaseSlots);
+}
+#endif
 
 extern "C" void gpu_sleep(double sleep_us, cudaStream_t stream) { sleep_kernel<<<1, 32, 0, stream>>>(sleep_us); }
