@@ -9,6 +9,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 
+#include "spmm_large_m.cuh"
 #include "spmm_small_m.cuh"
 
 namespace tsp {
@@ -47,13 +48,15 @@ static int device_sm_count() {
 // Launch-shape knobs, read once from the environment (for tuning runs):
 // TERNASPMM_CTAS_PER_SM_X10 (0 = automatic one-wave choice),
 // TERNASPMM_MAX_WARPS (cap on warps per CTA), TERNASPMM_PDL=0 to launch
-// without programmatic dependent launch.
+// without programmatic dependent launch, TERNASPMM_LARGE_MIN_M = smallest
+// token count sent to the tcgen05 kernel (default 33).
 struct Tuning {
-    int ctas_x10 = 0, max_warps = 0, pdl = 1;
+    int ctas_x10 = 0, max_warps = 0, pdl = 1, large_min_m = 33;
     Tuning() {
         if (const char* e = getenv("TERNASPMM_CTAS_PER_SM_X10")) ctas_x10 = atoi(e);
         if (const char* e = getenv("TERNASPMM_MAX_WARPS")) max_warps = atoi(e);
         if (const char* e = getenv("TERNASPMM_PDL")) pdl = atoi(e) != 0;
+        if (const char* e = getenv("TERNASPMM_LARGE_MIN_M")) large_min_m = atoi(e) > 0 ? atoi(e) : large_min_m;
     }
 };
 static const Tuning& tuning() {
@@ -133,6 +136,57 @@ static cudaError_t launch_small_m(SpmmParams& p, int token_blocks, int warp_slot
     return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
+// 2-D tensor map over the activations x[M][K] (int8): tiles of NT tokens x
+// 128 k, 128-byte swizzle, out-of-range rows and columns read as zero.
+static bool encode_x_map(CUtensorMap* map, const void* x, int M, int K, int NT) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess || !ptr)
+            return false;
+        fn = reinterpret_cast<EncodeFn>(ptr);
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)K};
+    const cuuint32_t box[2] = {(cuuint32_t)kLgKStep, (cuuint32_t)NT};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(x), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int NT>
+static cudaError_t launch_large_m(const SpmmParams& p, cudaStream_t stream) {
+    using L = LargeMSmem<NT>;
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    auto kern = spmm_large_m_kernel<NT>;
+    if (!attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
+        if (e != cudaSuccess) return e;
+        attr_done[dev] = true;
+    }
+    CUtensorMap map;
+    if (!encode_x_map(&map, p.x, p.M, p.K, NT)) return cudaErrorInvalidValue;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((p.N + 127) / 128, (p.M + NT - 1) / NT, 1);
+    cfg.blockDim = dim3(kLgThreads, 1, 1);
+    cfg.dynamicSmemBytes = L::total;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tuning().pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, p, map);
+}
+
 static void run_spmm(int8_t* x, uint64_t* bitmap, int* tile_off, uint16_t* quarter_off, uint32_t* signs, void* out,
                      __nv_bfloat16* s, __nv_bfloat16* ws, int ws_num, int M, int N, int K, int epilogue,
                      cudaStream_t stream) {
@@ -171,7 +225,10 @@ static void run_spmm(int8_t* x, uint64_t* bitmap, int* tile_off, uint16_t* quart
         return;
     }
     cudaError_t e;
-    if (M <= 8) {
+    if (M >= tuning().large_min_m) {
+        p.splits = 1;
+        e = M <= 64 ? launch_large_m<64>(p, stream) : (M <= 128 ? launch_large_m<128>(p, stream) : launch_large_m<256>(p, stream));
+    } else if (M <= 8) {
         e = launch_small_m<1, 16, 2>(p, 1, 32, stream);
     } else if (M <= 16) {
         e = launch_small_m<2, 16, 1>(p, 1, 16, stream);

@@ -244,3 +244,42 @@ def test_full_size_linearity_property(lib):
     assert (a1 + a2 == a12).all()
     acc, _ = c_oracle.ternaspmm(x1, w, np.full(M, 0x3F80, np.uint16), np.full(4, 0x3F80, np.uint16), 1)
     assert (a1 == acc).all()
+
+
+# ---- large token counts: the tcgen05 (tensor memory) kernel ------------------
+
+@pytest.mark.parametrize("M", [33, 64, 100, 128, 129, 256, 257, 512])
+@pytest.mark.parametrize("N,K", [(64, 64), (128, 128), (192, 320), (256, 1088)])
+def test_large_batch_accumulators_bit_exact(lib, M, N, K):
+    w = o.make_ternary(N, K, 0.45, seed=N + K + M)
+    xq = np.random.default_rng(M).integers(-128, 128, size=(M, K), dtype=np.int8)
+    assert (accumulate(lib, xq, Packed(w)) == o.gemm_i32(xq, w)).all()
+    assert lib.ternaspmm_last_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K,ws_num", [(256, 3840, 2560, 3), (300, 2560, 6912, 1), (64, 2560, 2560, 1),
+                                          (2048, 2560, 2560, 1), (130, 13824, 2560, 2)])
+def test_large_batch_layer_shapes_outputs(lib, M, N, K, ws_num):
+    check(lib, M, N, K, ws_num)
+
+
+@pytest.mark.parametrize("entry", ["bitlinear_TernaSpMM_decode", "bitlinear_TernaSpMM_prefill"])
+def test_large_batch_both_epilogues_and_segments(lib, entry):
+    check(lib, 96, 768, 256, 3, entry=entry)
+    check(lib, 160, 3840, 128, 3, entry=entry)
+    check(lib, 140, 192, 192, 2, entry=entry, p_zero=0.0)
+    check(lib, 140, 192, 192, 2, entry=entry, p_zero=1.0)
+
+
+def test_full_size_prefill_against_c_oracle(lib):
+    """BASELINE config 2's largest case: gate-up 2560 -> 13824 at 2048 tokens."""
+    N, K, M = 13824, 2560, 2048
+    w = o.make_ternary(N, K, 0.45, seed=61)
+    xq, s = o.make_activations(M, K, seed=62)
+    ws = o.make_ws(2, seed=63)
+    sb, wb = o.f32_to_bf16_bits(s.reshape(-1)), o.f32_to_bf16_bits(ws)
+    pk = Packed(w)
+    acc, want = c_oracle.ternaspmm(xq, w, sb, wb, 2)
+    assert (accumulate(lib, xq, pk) == acc).all()
+    got = call(lib, "bitlinear_TernaSpMM", xq, pk, sb, wb, 2)
+    assert (got == want).all()
