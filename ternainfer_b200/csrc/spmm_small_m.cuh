@@ -72,7 +72,8 @@ struct SmallMSmem {
     static constexpr int toff = red + MT * 8 * kRedStride * 4;    // int [kChunkTiles+1]
     static constexpr int qoff = toff + 80;                        // u16 [3*kChunkTiles]
     static constexpr int scl = qoff + 96;                         // float s[MT*8], ws[4]
-    static constexpr int bar = scl + (MT * 8 + 4) * 4;            // mbarrier
+    static constexpr int flag = scl + (MT * 8 + 4) * 4;           // int: bulk copies arrived
+    static constexpr int bar = flag + 8;                          // mbarrier
     static constexpr int bm = (bar + 16 + 127) / 128 * 128;       // bitmap chunk
     static constexpr int sg = bm + kChunkTiles * 512;             // sign chunk
     static constexpr int rest = (sg + kSignBufBytes + 127) / 128 * 128;
@@ -268,8 +269,16 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const Spm
             for (int c = 0; c < 4; ++c) acc[r][mt][c] = 0;
 
     const uint32_t lut_lane = lut_base | (uint32_t)(lane * 4);
+    // One warp polls the copy barrier; the others sleep at the CTA barrier
+    // instead of spending issue slots on polling.
+    volatile int* ok_flag = reinterpret_cast<volatile int*>(rest + L::flag);
     uint32_t phase = 0;
-    bool ok = mbar_wait_bounded(bar, phase);
+    if (warp == 0) {
+        const bool arrived = mbar_wait_bounded(bar, phase);
+        if (lane == 0) *ok_flag = arrived;
+    }
+    __syncthreads();
+    bool ok = *ok_flag != 0;
     phase ^= 1u;
     phase_mark(2);
 
@@ -340,7 +349,12 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const Spm
                 }
                 mbar_arrive(bar);
             }
-            ok = mbar_wait_bounded(bar, phase);
+            if (warp == 0) {
+                const bool arrived = mbar_wait_bounded(bar, phase);
+                if (lane == 0) *ok_flag = arrived;
+            }
+            __syncthreads();
+            ok = *ok_flag != 0;
             phase ^= 1u;
             if (!ok) break;
         }

@@ -231,7 +231,7 @@ static void run_spmm(int8_t* x, uint64_t* bitmap, int* tile_off, uint16_t* quart
     } else if (M <= 8) {
         e = launch_small_m<1, 16, 2>(p, 1, 32, stream);
     } else if (M <= 16) {
-        e = launch_small_m<2, 16, 1>(p, 1, 16, stream);
+        e = launch_small_m<2, 12, 2>(p, 1, 24, stream);
     } else {
         e = launch_small_m<4, 8, 2>(p, (M + 31) / 32, 16, stream);
     }
