@@ -118,6 +118,18 @@ void ternaspmm_accumulate_i32(int8_t* x, uint64_t* bitmap, int* tile_offsets,
                               int32_t* out, int M, int N, int K,
                               ternaspmm_stream_t stream);
 
+/* Same operator with explicit scale-segment boundaries instead of the
+ * reference's hard-coded rules (equal widths, or 2560/640/640 when N == 3840):
+ * output column n uses ws[(n >= seg1) + (n >= seg2) + (n >= seg3)], limited to
+ * ws_num-1; unused boundaries are ignored.  Needed for head-sharded QKV and
+ * for models whose q/k/v widths are not BitNet-2B's.  prefill_form: 0 = decode
+ * epilogue, 1 = prefill epilogue, -1 = by token count like bitlinear_TernaSpMM. */
+void ternaspmm_linear_segments(int8_t* x, uint64_t* bitmap, int* tile_offsets,
+                               uint16_t* quarter_offsets, uint32_t* sign_words,
+                               ternaspmm_bf16* out, ternaspmm_bf16* s, ternaspmm_bf16* ws,
+                               int ws_num, int M, int N, int K, int seg1, int seg2, int seg3,
+                               int prefill_form, ternaspmm_stream_t stream);
+
 /* Host packer from int8 ternary [N][K] into caller-provided arrays
  * (bitmap N*K/64, tile_offsets tiles+1, quarter_offsets 3*tiles, sign_words
  * at least N*K/32 + 4 words, zero-filled by the call).  Returns the number of

@@ -255,7 +255,7 @@ __global__ void __launch_bounds__(kLgThreads, 1)
         const bool n_ok = n < N;
         float ws_el = 0.f;
         if (p.epilogue != EPI_RAW_I32 && n_ok)
-            ws_el = __bfloat162float(p.ws[ws_group(n, N, p.ws_num, N / p.ws_num, p.epilogue)]);
+            ws_el = __bfloat162float(p.ws[ws_group(n, p)]);
         if (ok) {
 #pragma unroll 1
             for (int c0 = chalf * (NT / 2); c0 < (chalf + 1) * (NT / 2); c0 += 16) {

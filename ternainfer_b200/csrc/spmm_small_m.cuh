@@ -34,6 +34,8 @@ struct SpmmParams {
     const __nv_bfloat16* s;      // [M]
     const __nv_bfloat16* ws;     // [4]
     int ws_num, M, N, K, epilogue, splits;
+    int seg_b[3];   // first output column of scale segments 1, 2, 3 (INT_MAX when absent)
+    int seg_gran;   // 1, or the reference's granularity: 8 (decode form) / 128 (prefill form)
     int* status;
 };
 
@@ -96,25 +98,18 @@ __device__ __forceinline__ uint32_t lut_entry(uint32_t e) {
     return v;
 }
 
-// Scale-segment index of output column n.  Decode form: one group per 8
-// consecutive outputs, the 2560/640/640 split when ws_num == 3 and N == 3840
-// (Reduction_Kernel.cuh:42-54).  Prefill form: one group per 128 columns,
-// N == 3840 alone selects the split, clamped (epilogue_visitor_scale_ws.h:
-// 135-145).
-__device__ __forceinline__ int ws_group(int n, int N, int ws_num, int gw, int epilogue) {
-    int g;
-    // col / gw for gw = N / ws_num, limited to the four slots, without a division
-    if (epilogue == EPI_PREFILL) {
-        const int col = n & ~127;
-        if (N == 3840) g = col < 2560 ? 0 : (col < 3200 ? 1 : 2);
-        else g = (col >= gw) + (col >= 2 * gw) + (col >= 3 * gw);
-        g = min(g, ws_num - 1);
-    } else {
-        const int col = n & ~7;
-        if (ws_num == 3 && N == 3840) g = col < 2560 ? 0 : (col < 3200 ? 1 : 2);
-        else g = (col >= gw) + (col >= 2 * gw) + (col >= 3 * gw);
-    }
-    return g;
+// Scale-segment index of output column n.  The host turns the reference's
+// rules into three boundaries and a granularity: the decode form decides per
+// group of 8 outputs, equal widths N/ws_num or the 2560/640/640 split when
+// ws_num == 3 and N == 3840 (Reduction_Kernel.cuh:42-54); the prefill form
+// decides per 128 columns, N == 3840 alone selects the split, and the index is
+// clamped to ws_num-1 (epilogue_visitor_scale_ws.h:135-145).  Explicit
+// boundaries (sharded layers) use granularity 1.
+__device__ __forceinline__ int ws_group(int n, const SpmmParams& p) {
+    const int col = n & ~(p.seg_gran - 1);
+    const int g = (col >= p.seg_b[0]) + (col >= p.seg_b[1]) + (col >= p.seg_b[2]);
+    const int limit = (p.epilogue == EPI_PREFILL || p.seg_gran == 1) ? p.ws_num - 1 : 3;
+    return max(min(g, limit), 0);
 }
 
 __device__ __forceinline__ __nv_bfloat16 scale_epilogue(int acc, float s_el, float ws_el, int epilogue) {
@@ -405,7 +400,7 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const Spm
     if (rank != 0) return;
 
     // ---- epilogue (rank 0): scale and store
-    const int N = p.N, gw = N / p.ws_num;
+    const int N = p.N;
     for (int i = tid; i < mrows * 64; i += blockDim.x) {
         const int t = i >> 6, nl = i & 63;
         const int n = rt * 64 + nl;
@@ -415,7 +410,7 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const Spm
             reinterpret_cast<int*>(p.out)[o] = v;
         } else {
             const float s_el = scl_s[t];
-            const float ws_el = scl_s[MT * 8 + ws_group(n, N, p.ws_num, gw, p.epilogue)];
+            const float ws_el = scl_s[MT * 8 + ws_group(n, p)];
             reinterpret_cast<__nv_bfloat16*>(p.out)[o] = scale_epilogue(v, s_el, ws_el, p.epilogue);
         }
     }

@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <limits.h>
 #include <stdlib.h>
 
 #include "spmm_large_m.cuh"
@@ -189,7 +190,7 @@ static cudaError_t launch_large_m(const SpmmParams& p, cudaStream_t stream) {
 
 static void run_spmm(int8_t* x, uint64_t* bitmap, int* tile_off, uint16_t* quarter_off, uint32_t* signs, void* out,
                      __nv_bfloat16* s, __nv_bfloat16* ws, int ws_num, int M, int N, int K, int epilogue,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, const int* seg_bounds = nullptr) {
     t_host_status = ST_OK;
     if (M < 1 || N < 64 || K < 64 || (N % 64) || (K % 64) ||
         (epilogue != EPI_RAW_I32 && (ws_num < 1 || ws_num > 4))) {
@@ -219,6 +220,19 @@ static void run_spmm(int8_t* x, uint64_t* bitmap, int* tile_off, uint16_t* quart
     p.N = N;
     p.K = K;
     p.epilogue = epilogue;
+    if (seg_bounds) {   // explicit segment boundaries
+        for (int i = 0; i < 3; ++i) p.seg_b[i] = (i + 1 < ws_num) ? seg_bounds[i] : INT_MAX;
+        p.seg_gran = 1;
+    } else {            // the reference's rules, see ws_group()
+        const bool prefill = epilogue == EPI_PREFILL;
+        p.seg_gran = prefill ? 128 : 8;
+        if (N == 3840 && (prefill || ws_num == 3)) {
+            p.seg_b[0] = 2560, p.seg_b[1] = 3200, p.seg_b[2] = INT_MAX;
+        } else {
+            const int gw = ws_num > 0 ? N / ws_num : N;
+            p.seg_b[0] = gw, p.seg_b[1] = 2 * gw, p.seg_b[2] = 3 * gw;
+        }
+    }
     p.status = status_device_ptr();
     if (!p.status) {
         t_host_status = ST_LAUNCH;
@@ -298,6 +312,16 @@ extern "C" void ternaspmm_accumulate_i32(int8_t* x, uint64_t* bitmap, int* tile_
                                          cudaStream_t stream) {
     run_spmm(x, bitmap, tile_offsets, quarter_offsets, sign_words, out, nullptr, nullptr, 1, M, N, K, EPI_RAW_I32,
              stream);
+    checkLastCudaError(__LINE__);
+}
+
+extern "C" void ternaspmm_linear_segments(int8_t* x, uint64_t* bitmap, int* tile_offsets, uint16_t* quarter_offsets,
+                                         uint32_t* sign_words, __nv_bfloat16* out, __nv_bfloat16* s,
+                                         __nv_bfloat16* ws, int ws_num, int M, int N, int K, int seg1, int seg2,
+                                         int seg3, int prefill_form, cudaStream_t stream) {
+    const int b[3] = {seg1, seg2, seg3};
+    const int epi = prefill_form < 0 ? (M <= 64 ? EPI_DECODE : EPI_PREFILL) : (prefill_form ? EPI_PREFILL : EPI_DECODE);
+    run_spmm(x, bitmap, tile_offsets, quarter_offsets, sign_words, out, s, ws, ws_num, M, N, K, epi, stream, b);
     checkLastCudaError(__LINE__);
 }
 

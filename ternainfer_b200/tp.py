@@ -1,0 +1,188 @@
+"""Tensor-parallel sharding of the ternary linears (one process per GPU).
+
+The reference is single-GPU (``local_rank = 0`` is hard-coded, generate.py:361
+of Gu-J/TernaInfer); this is the sharding for models that do not fit or are
+too batch-heavy for one chip: the fused QKV and gate-up linears are split by
+output rows (column-parallel, no collective, activations replicated), the O
+and down linears by input columns (row-parallel, ONE all-reduce each).
+
+Row-parallel detail.  In front of ``wo`` / ``w2`` sit a sub-layer RMSNorm over
+the full width and the per-token absmax quantiser, both of which need
+cross-rank statistics.  Two modes:
+
+``single`` (default) - one collective per linear.  Each rank quantises its
+    un-normalised slice ``x_r * g_r`` with its *local* absmax, multiplies on the
+    GPU (int32 accumulators), divides by its own scale and appends its partial
+    sum of squares as one extra column; a single fp32 all-reduce of [M, N+1]
+    carries everything and the RMS factor and weight scale are applied after.
+    Mathematically identical to the unsharded layer, numerically within bf16
+    rounding of it (each rank rounds with its own scale).
+``exact`` - bit-identical to the unsharded layer: all-reduce the sum of
+    squares, normalise, all-reduce (max) the absmax, quantise with the global
+    scale, all-reduce the int32 accumulators, then apply the decode epilogue.
+    Three collectives, two of them a few hundred bytes.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Sequence
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from .convert import compress_weight
+from .lib import load_library
+
+
+# ----------------------------------------------------------------- sharding
+def shard_rows(w: torch.Tensor, segments: Sequence[int], rank: int, tp: int) -> torch.Tensor:
+    """Column-parallel shard: rank r keeps rows [r*len/tp, (r+1)*len/tp) of every
+    segment (q, k, v / gate, up), concatenated in segment order."""
+    out, start = [], 0
+    for seg in segments:
+        assert seg % tp == 0, "segment length must divide by the tensor-parallel size"
+        step = seg // tp
+        out.append(w[start + rank * step: start + (rank + 1) * step])
+        start += seg
+    return torch.cat(out, dim=0).contiguous()
+
+
+def shard_cols(w: torch.Tensor, rank: int, tp: int) -> torch.Tensor:
+    """Row-parallel shard: rank r keeps input columns [r*K/tp, (r+1)*K/tp)."""
+    K = w.shape[1]
+    assert K % (64 * tp) == 0, "K/tp must be a multiple of 64"
+    return w[:, rank * (K // tp):(rank + 1) * (K // tp)].contiguous()
+
+
+def shard_vector(v: torch.Tensor, rank: int, tp: int) -> torch.Tensor:
+    n = v.shape[0]
+    return v[rank * (n // tp):(rank + 1) * (n // tp)].contiguous()
+
+
+def local_segments(segments: Sequence[int], tp: int) -> List[int]:
+    return [s // tp for s in segments]
+
+
+# ------------------------------------------------------------ kernel calls
+def _accumulate_i32(xq: torch.Tensor, packed, N: int) -> torch.Tensor:
+    """int8 [M, K] x packed weight -> int32 accumulators [M, N] on the GPU."""
+    if not xq.is_cuda:
+        raise RuntimeError("the TernaSpMM library has no CPU path")
+    lib = load_library()
+    cv, tg, tm, bm = packed
+    M, K = xq.shape
+    out = torch.empty((M, N), dtype=torch.int32, device=xq.device)
+    lib.ternaspmm_accumulate_i32(xq.data_ptr(), bm.data_ptr(), tg.data_ptr(), tm.data_ptr(), cv.data_ptr(),
+                                 out.data_ptr(), M, N, K, torch.cuda.current_stream().cuda_stream)
+    return out
+
+
+def _linear_segments(xq, s, packed, ws, bounds, N: int) -> torch.Tensor:
+    if not xq.is_cuda:
+        raise RuntimeError("the TernaSpMM library has no CPU path")
+    lib = load_library()
+    cv, tg, tm, bm = packed
+    M, K = xq.shape
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=xq.device)
+    b = list(bounds) + [2 ** 31 - 1] * (3 - len(bounds))
+    lib.ternaspmm_linear_segments(xq.data_ptr(), bm.data_ptr(), tg.data_ptr(), tm.data_ptr(), cv.data_ptr(),
+                                  out.data_ptr(), s.data_ptr(), ws.data_ptr(), len(bounds) + 1, M, N, K,
+                                  b[0], b[1], b[2], -1, torch.cuda.current_stream().cuda_stream)
+    return out
+
+
+def _quant(x: torch.Tensor, amax: torch.Tensor = None):
+    if amax is None:
+        amax = x.abs().max(dim=-1, keepdim=True).values
+    s = 127 / amax.clamp(min=1e-5)
+    return (x * s).round().clamp(-128, 127).to(torch.int8), s
+
+
+# ------------------------------------------------------------------ modules
+class ColumnParallelSpBitLinear(nn.Module):
+    """Rows of a fused linear owned by this rank.  ``dic[key + '.weight_*']``
+    already hold the rank's packed shard; ``dic[key + '.weight_segments']`` the
+    local segment lengths (e.g. [q/tp, k/tp, v/tp])."""
+
+    def __init__(self, in_features: int, out_features: int, dic: dict, key: str):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        dev = "cuda" if torch.cuda.is_available() else "cpu"
+        self.packed = [dic[key + s].to(dev) for s in (".weight_compressed_val", ".weight_TileOffsets_global",
+                                                      ".weight_TileOffsets_median", ".weight_bitmap")]
+        self.weight_scale = dic[key + ".weight_scale"].to(dev)
+        segs = [int(v) for v in dic[key + ".weight_segments"]]
+        assert sum(segs) == out_features
+        self.bounds = [sum(segs[:i + 1]) for i in range(len(segs) - 1)]
+
+    def forward(self, x):
+        shape = list(x.shape[:-1]) + [self.out_features]
+        xq, s = _quant(x.reshape(-1, self.in_features))
+        y = _linear_segments(xq, s.to(torch.bfloat16).contiguous(), self.packed, self.weight_scale, self.bounds,
+                             self.out_features)
+        return y.reshape(shape)
+
+
+class RowParallelSpBitLinear(nn.Module):
+    """Input-column shard of ``wo`` / ``w2`` with the preceding sub-layer norm
+    folded in (see the module docstring).  ``norm_weight`` is this rank's slice
+    of the norm weight; ``in_features`` is the local width K/tp."""
+
+    def __init__(self, in_features: int, out_features: int, dic: dict, key: str, group=None,
+                 norm_weight: torch.Tensor = None, eps: float = 1e-5, mode: str = "single"):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        dev = "cuda" if torch.cuda.is_available() else "cpu"
+        self.packed = [dic[key + s].to(dev) for s in (".weight_compressed_val", ".weight_TileOffsets_global",
+                                                      ".weight_TileOffsets_median", ".weight_bitmap")]
+        self.ws = dic[key + ".weight_scale"].to(dev).float()[0]
+        self.norm_weight = norm_weight.to(dev).float()
+        self.group, self.eps, self.mode = group, eps, mode
+        self.tp = dist.get_world_size(group) if dist.is_initialized() else 1
+
+    def forward(self, x):
+        shape = list(x.shape[:-1]) + [self.out_features]
+        x2 = x.reshape(-1, self.in_features)
+        full_width = self.in_features * self.tp
+        xf = x2.float()
+        ss = xf.pow(2).sum(-1, keepdim=True)
+        if self.mode == "exact":
+            if self.tp > 1:
+                dist.all_reduce(ss, group=self.group)
+            y = (xf * torch.rsqrt(ss / full_width + self.eps) * self.norm_weight).to(x.dtype)
+            amax = y.abs().max(dim=-1, keepdim=True).values
+            if self.tp > 1:
+                dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=self.group)
+            xq, s = _quant(y, amax)
+            acc = _accumulate_i32(xq, self.packed, self.out_features)
+            if self.tp > 1:
+                dist.all_reduce(acc, group=self.group)
+            out = (acc.float() / s.float() * self.ws).to(torch.bfloat16)
+        else:
+            z = (xf * self.norm_weight).to(x.dtype)               # un-normalised: the RMS factor is applied last
+            xq, s = _quant(z)
+            acc = _accumulate_i32(xq, self.packed, self.out_features)
+            buf = torch.cat([acc.float() / s.float(), ss], dim=1)  # [M, N+1]: partial outputs + partial sum of squares
+            if self.tp > 1:
+                dist.all_reduce(buf, group=self.group)             # the one collective of this linear
+            rstd = torch.rsqrt(buf[:, -1:] / full_width + self.eps)
+            out = (buf[:, :-1] * rstd * self.ws).to(torch.bfloat16)
+        return out.reshape(shape)
+
+
+# ------------------------------------------------- sharded checkpoint helper
+def shard_checkpoint_entry(dic: dict, key: str, w_int8: torch.Tensor, ws: torch.Tensor, segments, kind: str,
+                           rank: int, tp: int):
+    """Pack this rank's shard of one ternary weight into ``dic`` under ``key``
+    (``kind`` = 'column' or 'row')."""
+    if kind == "column":
+        local = shard_rows(w_int8, segments, rank, tp)
+        dic[key + ".weight_segments"] = torch.tensor(local_segments(segments, tp))
+    else:
+        local = shard_cols(w_int8, rank, tp)
+    cv, tg, tm, bm = compress_weight(local)
+    dic[key + ".weight_compressed_val"], dic[key + ".weight_TileOffsets_global"] = cv, tg
+    dic[key + ".weight_TileOffsets_median"], dic[key + ".weight_bitmap"] = tm, bm
+    dic[key + ".weight_scale"] = ws
+    return local

@@ -79,3 +79,18 @@ def test_reference_known_answer_on_reference_kernels(ref):
     got = run_reference(ref, w, np.ones((M, K), np.int8), one, o.f32_to_bf16_bits(np.ones(4, np.float32)), 4, 7)
     want = o.bf16_round(w.sum(axis=1, dtype=np.int32).astype(np.float32))
     assert np.abs(o.bf16_bits_to_f32(got) - want[None, :]).sum() == 0.0
+
+
+@pytest.mark.parametrize("args", [["8", "2560", "2560", "45", "7"], ["16", "3840", "2560", "45", "7"],
+                                  ["64", "2560", "6912", "45", "7"], ["256", "2560", "2560", "45", "7"]])
+def test_reference_kernel_test_program_unchanged(args):
+    """tests/test_kernel.cu of the reference, compiled unchanged and linked against this
+    library (oracle/Makefile): its cuBLAS comparison must report TotalError 0.00."""
+    import subprocess
+    exe = os.path.join(os.path.dirname(REF_SO), "test_kernel")
+    if not os.path.exists(exe):
+        pytest.skip("oracle/_ref/test_kernel not built (needs the reference checkout at build time)")
+    r = subprocess.run([exe] + args, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    line = [l for l in r.stdout.splitlines() if l.startswith("TernaSpMM")]
+    assert line and "TotalError: 0.00" in line[0], r.stdout

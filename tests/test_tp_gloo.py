@@ -1,0 +1,116 @@
+"""CPU, world_size 2 (gloo): the tensor-parallel sharding and collective logic.
+The GPU kernel calls are replaced by the CPU oracle so that only the host logic
+(sharding, segment boundaries, statistics exchange, all-reduce) is under test."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import ternaspmm_oracle as o
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _oracle_accumulate(xq, packed, N):
+    cv, tg, tm, bm = [p.numpy() for p in packed]
+    K = xq.shape[1]
+    w = o.decode_weight_b200(cv, tg, tm, bm, N, K)
+    return torch.from_numpy(o.gemm_i32(xq.numpy(), w))
+
+
+def _oracle_linear_segments(xq, s, packed, ws, bounds, N):
+    acc = _oracle_accumulate(xq, packed, N).numpy()
+    col = np.arange(N)
+    g = sum((col >= b).astype(np.int64) for b in bounds) if bounds else np.zeros(N, np.int64)
+    wsf = ws.float().numpy()[g][None, :]
+    v = (acc.astype(np.float32) / s.float().numpy().reshape(-1, 1)).astype(np.float32) * wsf
+    return torch.from_numpy(o.f32_to_bf16_bits(v).view(np.int16)).view(torch.bfloat16)
+
+
+def _worker(rank, world, port, mode, q):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from ternainfer_b200 import tp
+    tp._accumulate_i32, tp._linear_segments = _oracle_accumulate, _oracle_linear_segments
+    torch.manual_seed(0)
+    dim, H, Hkv, D, ffn, M = 256, 4, 2, 64, 512, 5
+    x = torch.randn(M, dim).to(torch.bfloat16)
+    res = {}
+    # ---- column-parallel QKV with unequal segments, then gather and compare with the unsharded layer
+    segs = [H * D, Hkv * D, Hkv * D]
+    wqkv = torch.from_numpy(o.make_ternary(sum(segs), dim, 0.45, 1))
+    ws = torch.tensor([0.02, 0.03, 0.04, 0.0]).to(torch.bfloat16)
+    dic = {}
+    tp.shard_checkpoint_entry(dic, "qkv", wqkv, ws, segs, "column", rank, world)
+    col = tp.ColumnParallelSpBitLinear(dim, sum(segs) // world, dic, "qkv")
+    y_local = col(x)
+    gathered = [torch.empty_like(y_local) for _ in range(world)]
+    dist.all_gather(gathered, y_local)
+    full = {}
+    tp.shard_checkpoint_entry(full, "qkv", wqkv, ws, segs, "column", 0, 1)
+    y_full = tp.ColumnParallelSpBitLinear(dim, sum(segs), full, "qkv")(x)
+    # reassemble: rank r holds [q_r, k_r, v_r]
+    loc = tp.local_segments(segs, world)
+    parts = []
+    for si in range(3):
+        for r in range(world):
+            st = sum(loc[:si])
+            parts.append(gathered[r][:, st:st + loc[si]])
+    res["column_equal"] = bool(torch.equal(torch.cat(parts, dim=1), y_full))
+    # ---- row-parallel down projection
+    w2 = torch.from_numpy(o.make_ternary(dim, ffn, 0.45, 2))
+    g = (1 + 0.05 * torch.randn(ffn)).to(torch.bfloat16)
+    inner = torch.randn(M, ffn).to(torch.bfloat16)
+    ws2 = torch.tensor([0.025, 0, 0, 0]).to(torch.bfloat16)
+    dic2, one = {}, {}
+    tp.shard_checkpoint_entry(dic2, "w2", w2, ws2, None, "row", rank, world)
+    tp.shard_checkpoint_entry(one, "w2", w2, ws2, None, "row", 0, 1)
+    row = tp.RowParallelSpBitLinear(ffn // world, dim, dic2, "w2", None, tp.shard_vector(g, rank, world), 1e-5, mode)
+    y = row(tp.shard_vector(inner.t().contiguous(), rank, world).t().contiguous())
+    ref = tp.RowParallelSpBitLinear(ffn, dim, one, "w2", None, g, 1e-5, "exact")
+    ref.tp = 1
+    y_ref = ref(inner)
+    res["row_equal"] = bool(torch.equal(y, y_ref))
+    res["row_max_rel"] = float((y.float() - y_ref.float()).abs().max() / y_ref.float().pow(2).mean().sqrt())
+    if rank == 0:
+        q.put(res)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["exact", "single"])
+def test_two_rank_tensor_parallel_linears(mode):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, mode, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert res["column_equal"]
+    if mode == "exact":
+        assert res["row_equal"], res      # bit-identical to the unsharded layer
+    else:
+        assert res["row_max_rel"] < 0.05, res   # one collective: max error under 5 % of the output RMS (quantisation noise)
+
+
+def test_shard_helpers():
+    from ternainfer_b200 import tp
+    w = torch.arange(12 * 128).reshape(12, 128)
+    a = tp.shard_rows(w, [8, 2, 2], 1, 2)
+    assert a.shape == (6, 128) and torch.equal(a[:4], w[4:8]) and torch.equal(a[4], w[9]) and torch.equal(a[5], w[11])
+    b = tp.shard_cols(w, 1, 2)
+    assert torch.equal(b, w[:, 64:])
+    with pytest.raises(AssertionError):
+        tp.shard_rows(w, [7, 3, 2], 0, 2)
