@@ -353,9 +353,160 @@ def run_gpu_arm(args):
             "gpu_launches": launches * args.steps,
             "clocks": clocks,
         }
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
+    _finish(world)
+
+
+# ----------------------------------------------------------------------------
+# Tensor-parallel arm (BASELINE config 5 shapes): hidden 8192, 64/8 heads,
+# ffn 28672, batch 64.  Per layer: QKV and gate-up column-parallel, O and down
+# row-parallel with ONE all-reduce each; the attention itself is not part of
+# the path and is skipped (its output is a fixed synthetic tensor).  Strong
+# scaling: the model is fixed, each rank holds 1/N of every weight.
+# ----------------------------------------------------------------------------
+
+def run_tp_arm(args):
+    import torch
+    import torch.distributed as dist
+    from ternainfer_b200 import load_library, tp
+    from ternainfer_b200.convert import compress_weight, compressed_nbytes
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
     if world > 1:
-        dist.destroy_process_group()
+        dist.init_process_group("nccl", device_id=device)
+    load_library()
+    dim, H, Hkv, D, ffn, M = 8192, 64, 8, 128, 28672, args.tokens if args.tokens != 8 else 64
+    L = args.layers if args.layers != 30 else 4
+    gen = torch.Generator(device=device)
+
+    def tern(n, k, seed):
+        gen.manual_seed(seed)
+        r = torch.rand((n, k), generator=gen, device=device)
+        sign = torch.randint(0, 2, (n, k), generator=gen, device=device, dtype=torch.int8) * 2 - 1
+        return torch.where(r < P_ZERO, torch.zeros((), dtype=torch.int8, device=device), sign)
+
+    layers, wbytes = [], 0
+    for li in range(L):
+        dic = {}
+        specs = [("wqkv", "column", (H + 2 * Hkv) * D // world, dim, [H * D // world, Hkv * D // world, Hkv * D // world]),
+                 ("wo", "row", dim, dim // world, None),
+                 ("w13", "column", 2 * ffn // world, dim, [ffn // world, ffn // world]),
+                 ("w2", "row", dim, ffn // world, None)]
+        for si, (name, kind, n, k, segs) in enumerate(specs):
+            w = tern(n, k, args.seed + 100003 * rank + 101 * li + si)
+            cv, tg, tm, bm = compress_weight(w)
+            wbytes += compressed_nbytes(cv, tg, tm, bm)
+            dic[name + ".weight_compressed_val"], dic[name + ".weight_TileOffsets_global"] = cv, tg
+            dic[name + ".weight_TileOffsets_median"], dic[name + ".weight_bitmap"] = tm, bm
+            ws = torch.zeros(4, device=device)
+            ws[:len(segs) if segs else 1] = 0.02
+            dic[name + ".weight_scale"] = ws.to(torch.bfloat16)
+            if segs:
+                dic[name + ".weight_segments"] = torch.tensor(segs)
+            del w
+        ones_d = torch.ones(dim // world, device=device)
+        ones_f = torch.ones(ffn // world, device=device)
+        layers.append((tp.ColumnParallelSpBitLinear(dim, specs[0][2], dic, "wqkv"),
+                       tp.RowParallelSpBitLinear(dim // world, dim, dic, "wo", None, ones_d, 1e-5, args.tp_mode),
+                       tp.ColumnParallelSpBitLinear(dim, specs[2][2], dic, "w13"),
+                       tp.RowParallelSpBitLinear(ffn // world, dim, dic, "w2", None, ones_f, 1e-5, args.tp_mode)))
+    gen.manual_seed(args.seed)
+    x0 = torch.randn((M, dim), generator=gen, device=device).to(torch.bfloat16)
+    attn = torch.randn((M, dim // world), generator=gen, device=device).to(torch.bfloat16)
+    if world > 1:
+        dist.broadcast(x0, 0)
+
+    def step():
+        x = x0
+        for qkv, wo, w13, w2 in layers:
+            qkv(x)
+            h = x + wo(attn)
+            x1, x3 = w13(h).chunk(2, -1)
+            x = h + w2(torch.relu(x1) ** 2 * x3)
+        return x
+
+    def log(msg):
+        if rank == 0 and args.verbose:
+            print("[tp] " + msg, file=sys.stderr, flush=True)
+
+    class _Eager:
+        def replay(self):
+            step()
+
+    stream = torch.cuda.Stream(device=device)
+    with torch.cuda.stream(stream):
+        log("weights built; eager warm-up")
+        for _ in range(2):
+            step()
+        stream.synchronize()
+        log("eager steps done")
+        if args.no_graph:
+            graph = _Eager()
+        else:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                y = step()
+            log("graph captured")
+        for _ in range(args.warmup):
+            graph.replay()
+        log("warm-up replays done")
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
+    wb = torch.tensor([float(wbytes)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(wb)
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        ms = float(t.item())
+        peak, kind = measured_peak()
+        val = float(wb.item()) * args.steps / (ms * 1e-3) / 1e9
+        line = {"metric": "ternaspmm_tp_compressed_weight_GBps", "value": val, "unit": "GB/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "int8xternary->int32->bf16", "data": "synthetic",
+                "config": {"workload": f"tp_linear_stack_8192x28672_bs{M}", "layers": L, "tokens": M, "tp": world,
+                           "row_parallel_mode": args.tp_mode, "collective": "one NCCL all-reduce per row-parallel linear"
+                           if args.tp_mode == "single" else "three all-reduces per row-parallel linear (bit-exact mode)",
+                           "l2_policy": "inputs larger than L2: %.0f MB of weights per step over all ranks" % (wb.item() / 1e6)},
+                "roofline": {"bound": "hbm", "achieved": val / world, "peak": peak, "unit": "GB/s",
+                             "frac": val / world / peak, "peak_kind": "of " + kind, "traffic": None,
+                             "note": "per-GPU compressed-weight bytes per second"},
+                "gpu_launches": 4 * L * args.steps, "clocks": clocks}
+        print(json.dumps(line), flush=True)
+    _finish(world)
+
+
+def _finish(world):
+    """Leave without tearing NCCL down: destroying a process group while CUDA
+    graphs that hold NCCL kernels are alive blocks at exit, so every rank meets
+    at a barrier, flushes and exits the process directly."""
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
@@ -367,10 +518,16 @@ def main():
     ap.add_argument("--tokens", type=int, default=8)
     ap.add_argument("--layers", type=int, default=30)
     ap.add_argument("--seed", type=int, default=1234)
+    ap.add_argument("--workload", default="sweep", choices=["sweep", "tp"])
+    ap.add_argument("--tp_mode", default="single", choices=["single", "exact"])
+    ap.add_argument("--no_graph", action="store_true", help="tp workload: launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--verbose", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "tp":
+        run_tp_arm(args)
     else:
         run_gpu_arm(args)
 

@@ -11,16 +11,17 @@
 //
 // CTA tile: 128 weight rows (the MMA's M) x NT tokens (the MMA's N) x all of
 // K, 128 k per pipeline stage.  Warp roles:
-//   warps 0-7  decoders: warp w owns the 64x64 weight tile (row half w&1,
-//              k half (w>>1)&1) of every second k-step; it reads bitmaps,
+//   warps 0-15 decoders: two warps share the 64x64 weight tile (row half,
+//              k half) of every second k-step, each taking two of the four
+//              16-row groups; they read bitmaps,
 //              offsets and sign words from global memory, decodes with the
 //              same table lookup as the small-batch kernel and stores int8
 //              rows of 128 k in the 128-byte-swizzled K-major layout.  After
 //              the K loop the same warps are the epilogue (tcgen05.ld ->
 //              scale -> bf16 store).
-//   warp 8     activation loader: one thread issues 2-D TMA tile loads of
+//   warp 16    activation loader: one thread issues 2-D TMA tile loads of
 //              x[NT tokens][128 k] (128-byte swizzle, no multicast).
-//   warp 9     one thread issues tcgen05.mma (four K=32 steps per stage) and
+//   warp 17    one thread issues tcgen05.mma (four K=32 steps per stage) and
 //              commits stage releases / the final accumulator barrier.
 // All hand-offs are mbarriers; every wait has an iteration limit and a CTA-wide
 // abort flag so that a lost signal ends the kernel with a status word.
@@ -31,7 +32,7 @@
 
 namespace tsp {
 
-constexpr int kLgDecoders = 8;
+constexpr int kLgDecoders = 16;          // two warps per 64x64 tile, two k-steps in flight
 constexpr int kLgThreads = (kLgDecoders + 2) * 32;
 constexpr int kLgKStep = 128;            // k per pipeline stage = one 128-byte swizzle row
 constexpr int kLgAStage = 128 * 128;     // bytes: 128 rows x 128 k int8
@@ -139,7 +140,7 @@ __global__ void __launch_bounds__(kLgThreads, 1)
     // ---- set-up
     if (tid == 0) {
         for (int s = 0; s < 4; ++s) {
-            mbar_init(bar_full_a(s), 4);   // the four decoder warps of a stage
+            mbar_init(bar_full_a(s), 8);   // the eight decoder warps of a stage
             mbar_init(bar_full_b(s), 1);   // the loader thread (+ TMA bytes)
             mbar_init(bar_empty(s), 1);    // tcgen05.commit
         }
@@ -193,41 +194,74 @@ __global__ void __launch_bounds__(kLgThreads, 1)
         }
     } else {
         // ---------------------------------------------------------- decoders
-        const int half = warp & 1, kk = (warp >> 1) & 1, grp = warp >> 2;
+        const int sub = warp & 1, half = (warp >> 1) & 1, kk = (warp >> 2) & 1, grp = warp >> 3;
         const int g = lane >> 2, q = lane & 3;
         const int rt = rb * 2 + half;
         const bool have_rows = rt * 64 < N;
         const uint32_t lut_lane = lut_base | (uint32_t)(lane * 4);
+        // Register pipeline over this warp's tiles (k-steps grp, grp+2, ...):
+        //   stage A  bitmap words + offsets of the tile two steps ahead
+        //   stage B  sign-stream position and the eight sign words of the next tile
+        //   stage C  decode the current tile and store it
+        // so the three dependent global round trips of a tile overlap the
+        // decoding of the two tiles before it.
+        struct Head { uint4 bw; int toff, qbase; bool valid; };
+        struct Signs { uint32_t lo[2], hi[2], sh[2]; };   // this warp's two bitmap words: 2*sub, 2*sub+1
+        auto load_head = [&](int ks) {
+            Head h;
+            const int kt = ks * 2 + kk;
+            h.valid = have_rows && ks < KS && kt < KT;
+            h.bw = make_uint4(0, 0, 0, 0), h.toff = 0, h.qbase = 0;
+            if (h.valid) {
+                const long long T = (long long)rt * KT + kt;
+                h.bw = __ldg(reinterpret_cast<const uint4*>(p.bitmap + T * 128) + lane);
+                h.toff = __ldg(p.tile_off + T);
+                const int qd = lane >> 3;
+                h.qbase = qd ? (int)__ldg(p.quarter_off + 3 * T + qd - 1) : 0;
+            }
+            return h;
+        };
+        auto load_signs = [&](const Head& h) {
+            Signs sg;
+            const uint32_t w[4] = {h.bw.x, h.bw.y, h.bw.z, h.bw.w};
+            int cnt[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) cnt[r] = __popc(w[r]);
+            const int tot = cnt[0] + cnt[1] + cnt[2] + cnt[3];
+            int incl = tot;
+#pragma unroll
+            for (int d = 1; d < 8; d <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, incl, d, 8);
+                if ((lane & 7) >= d) incl += t;
+            }
+            long long pos = (long long)h.toff + h.qbase + incl - tot + (sub ? cnt[0] + cnt[1] : 0);
+            const int mine[2] = {sub ? cnt[2] : cnt[0], sub ? cnt[3] : cnt[1]};
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const uint32_t* sw = p.signs + (pos >> 5);
+                sg.lo[r] = h.valid ? __ldg(sw) : 0u;
+                sg.hi[r] = h.valid ? __ldg(sw + 1) : 0u;
+                sg.sh[r] = (uint32_t)pos & 31u;
+                pos += mine[r];
+            }
+            return sg;
+        };
+        Head h_cur = load_head(grp), h_nxt = load_head(grp + 2);
+        Signs s_cur = load_signs(h_cur);
         for (int ks = grp; ks < KS && ok; ks += 2) {
             const int s = ks % ST, it = ks / ST;
+            const Head h_far = load_head(ks + 4);      // stage A
+            const Signs s_nxt = load_signs(h_nxt);     // stage B
             if (it > 0) ok = wait_or_abort(bar_empty(s), (it - 1) & 1, abort_flag);
             if (!ok) break;
-            const int kt = ks * 2 + kk;
-            if (have_rows && kt < KT) {
-                const long long T = (long long)rt * KT + kt;
-                const uint4 bw = __ldg(reinterpret_cast<const uint4*>(p.bitmap + T * 128) + lane);
-                const uint32_t w[4] = {bw.x, bw.y, bw.z, bw.w};
-                int cnt[4];
-#pragma unroll
-                for (int r = 0; r < 4; ++r) cnt[r] = __popc(w[r]);
-                const int tot = cnt[0] + cnt[1] + cnt[2] + cnt[3];
-                int incl = tot;
-#pragma unroll
-                for (int d = 1; d < 8; d <<= 1) {
-                    const int t = __shfl_up_sync(0xffffffffu, incl, d, 8);
-                    if ((lane & 7) >= d) incl += t;
-                }
-                const int qd = lane >> 3;
-                const int qbase = qd ? (int)__ldg(p.quarter_off + 3 * T + qd - 1) : 0;
-                long long pos = (long long)__ldg(p.tile_off + T) + qbase + incl - tot;
+            if (h_cur.valid) {                         // stage C
+                const uint32_t w[2] = {sub ? h_cur.bw.z : h_cur.bw.x, sub ? h_cur.bw.w : h_cur.bw.y};
                 const uint32_t a_stage = sbase + L::a + s * kLgAStage;
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    const uint32_t* sw = p.signs + (pos >> 5);
-                    const uint32_t sgn = __funnelshift_r(__ldg(sw), __ldg(sw + 1), (uint32_t)pos & 31u);
-                    pos += cnt[r];
+                for (int rr = 0; rr < 2; ++rr) {
+                    const int r = 2 * sub + rr;
                     uint32_t a[8];
-                    decode_word(w[r], sgn, lut_lane, a);
+                    decode_word(w[rr], __funnelshift_r(s_cur.lo[rr], s_cur.hi[rr], s_cur.sh[rr]), lut_lane, a);
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const int row = 64 * half + 16 * r + 8 * h + g;          // row & 7 == g
@@ -239,6 +273,7 @@ __global__ void __launch_bounds__(kLgThreads, 1)
             fence_proxy_async_smem();   // generic-proxy stores -> visible to the tensor core's async proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_full_a(s));
+            h_cur = h_nxt, h_nxt = h_far, s_cur = s_nxt;
         }
 
         // ---------------------------------------------------------- epilogue
@@ -250,7 +285,7 @@ __global__ void __launch_bounds__(kLgThreads, 1)
         if (ok) ok = wait_or_abort(bar_acc, 0, abort_flag);
         ok = __all_sync(0xffffffffu, ok);   // the tensor-memory loads below are warp-collective
         tc_fence_after();
-        const int quarter = warp & 3, chalf = warp >> 2;
+        const int quarter = warp & 3, cpart = warp >> 2;   // TMEM lane quarter (= warp % 4) and column quarter
         const int n = rb * 128 + 32 * quarter + lane;
         const bool n_ok = n < N;
         float ws_el = 0.f;
@@ -258,7 +293,7 @@ __global__ void __launch_bounds__(kLgThreads, 1)
             ws_el = __bfloat162float(p.ws[ws_group(n, p)]);
         if (ok) {
 #pragma unroll 1
-            for (int c0 = chalf * (NT / 2); c0 < (chalf + 1) * (NT / 2); c0 += 16) {
+            for (int c0 = cpart * (NT / 4); c0 < (cpart + 1) * (NT / 4); c0 += 16) {
                 int v[16];
                 tmem_ld16(tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)c0, v);
 #pragma unroll

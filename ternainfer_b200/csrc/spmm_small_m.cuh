@@ -6,14 +6,18 @@
 //
 // Work split: blockIdx.y = 64-row tile of the weight, blockIdx.x = K split
 // (the CTAs of one row tile form a thread-block cluster), blockIdx.z = block
-// of MT*8 tokens.  Each CTA streams its compressed k-tiles into shared memory
-// with 1-D bulk async copies completing on an mbarrier, each warp decodes
-// whole 64x64 tiles (bitmap popcount prefix -> sign window -> 256-entry
-// lookup of 4 int8 weights) straight into int8 MMA A fragments and multiplies
-// them with the activation fragments, partial sums are combined across warps
-// in shared memory and across the cluster through distributed shared memory,
-// and the cluster's first CTA applies the scale epilogue and stores bf16.
-// The int32 workspace of the reference is not needed.
+// of MT*8 tokens.  Every warp owns whole 64x64 tiles and runs decoupled from
+// the other warps: it streams its tiles' bitmap words (one coalesced 128-bit
+// load per lane), offsets and sign words from global memory through a
+// register pipeline (bitmaps two tiles ahead, sign words one tile ahead),
+// decodes them (bitmap popcount prefix -> sign windows -> two 256-entry
+// lookup tables of 4 int8 weights) straight into int8 MMA A fragments and
+// multiplies them with activation fragments read from L2.  The first tile of
+// every warp is decoded before the programmatic-dependency wait, since
+// weights never depend on the previous kernel.  Partial sums are combined
+// across warps in shared memory and across the cluster through distributed
+// shared memory; the cluster's first CTA applies the scale epilogue and
+// stores bf16.  The int32 workspace of the reference is not needed.
 #pragma once
 #include <cuda_bf16.h>
 
@@ -39,9 +43,8 @@ struct SpmmParams {
     int* status;
 };
 
-constexpr int kChunkTiles = 16;                    // k-tiles resident in shared memory at once
-constexpr int kLutBytes = 256 * 32 * 4;            // one copy of the table per lane (bank = lane)
-constexpr int kSignBufBytes = kChunkTiles * 512 + 64;
+constexpr int kLutBytes = 256 * 32 * 4;            // one copy of a table per lane (bank = lane)
+constexpr int kLut2Bytes = 2 * kLutBytes;          // lower-nibble table + upper-nibble table
 constexpr int kPreTiles = 1;                       // tiles per warp decoded into registers before the dependency wait
 
 // Phase timestamps for tuning builds (-DTSP_PHASE_TIMERS): thread 0 of every
@@ -63,24 +66,17 @@ __device__ __forceinline__ void phase_mark(int) {}
 
 constexpr int kRedStride = 68;                     // ints per token row of the reduction buffer (conflict-free)
 
-// Shared-memory plan.  The lookup table must start on a 32 KB boundary of the
-// shared window (its entry index is OR-ed into the address), which the
-// dynamic segment's base does not guarantee; the other buffers ("rest") go
-// into the gap in front of the table when it is large enough, else behind it.
+// Shared-memory plan.  The lookup tables must start on a 32 KB boundary of the
+// shared window (the entry index is OR-ed into the address), which the
+// dynamic segment's base does not guarantee; the small buffers ("rest") go
+// into the gap in front of the tables when it is large enough, else behind.
 template <int MT>
 struct SmallMSmem {
-    static constexpr int lut1 = 0;                                // the 256 entries, one copy
-    static constexpr int red = lut1 + 1024;                       // int32 [MT*8][kRedStride]
-    static constexpr int toff = red + MT * 8 * kRedStride * 4;    // int [kChunkTiles+1]
-    static constexpr int qoff = toff + 80;                        // u16 [3*kChunkTiles]
-    static constexpr int scl = qoff + 96;                         // float s[MT*8], ws[4]
-    static constexpr int flag = scl + (MT * 8 + 4) * 4;           // int: bulk copies arrived
-    static constexpr int bar = flag + 8;                          // mbarrier
-    static constexpr int bm = (bar + 16 + 127) / 128 * 128;       // bitmap chunk
-    static constexpr int sg = bm + kChunkTiles * 512;             // sign chunk
-    static constexpr int rest = (sg + kSignBufBytes + 127) / 128 * 128;
-    static constexpr int total = kLutBytes + 2 * rest + 128;      // worst case of the run-time placement
-    static_assert(2 * rest >= kLutBytes, "placement bound assumes the gap never exceeds twice the rest region");
+    static constexpr int lut1 = 0;                                // the 2 x 256 entries, one copy
+    static constexpr int red = lut1 + 2048;                       // int32 [MT*8][kRedStride]
+    static constexpr int scl = red + MT * 8 * kRedStride * 4;     // float s[MT*8], ws[4]
+    static constexpr int rest = (scl + (MT * 8 + 4) * 4 + 127) / 128 * 128;
+    static constexpr int total = kLut2Bytes + kLutBytes + rest;   // worst case of the run-time placement
 };
 
 // Four int8 weights of one bitmap nibble: bit j of `nib` set -> weight j is
@@ -123,32 +119,53 @@ __device__ __forceinline__ __nv_bfloat16 scale_epilogue(int acc, float s_el, flo
     return __float2bfloat16_rn(v);
 }
 
-// Sign-stream position (in bits, relative to the chunk's first loaded word) of
-// this lane's first non-zero of tile i, plus the lane's four bitmap words.
+// One 64x64 tile as a warp sees it while it is in flight: the lane's four
+// bitmap words and the tile's offsets (TileHead, loaded two tiles ahead), then
+// the lane's eight sign words (TileSigns, loaded one tile ahead).
 struct TileHead {
-    uint32_t w[4];
-    int cnt[4];
-    int pos;
+    uint4 bw;
+    int toff, qbase;
+};
+struct TileSigns {
+    uint32_t lo[4], hi[4];
+    int pos;      // bit position of the lane's first sign in the stream (its low 5 bits are the first shift)
 };
 
-__device__ __forceinline__ TileHead tile_head(uint32_t bm_tile, const int* toff_s, const uint16_t* qoff_s, int i,
-                                              int w_first, int lane) {
+__device__ __forceinline__ TileHead load_head(const SpmmParams& p, long long tile, bool valid, int lane) {
     TileHead h;
-    const uint4 bw = lds128(bm_tile + lane * 16);
-    h.w[0] = bw.x, h.w[1] = bw.y, h.w[2] = bw.z, h.w[3] = bw.w;
-#pragma unroll
-    for (int r = 0; r < 4; ++r) h.cnt[r] = __popc(h.w[r]);
-    const int tot = h.cnt[0] + h.cnt[1] + h.cnt[2] + h.cnt[3];
-    int incl = tot;  // inclusive prefix over the 8 lanes of this quarter
+    h.bw = make_uint4(0, 0, 0, 0), h.toff = 0, h.qbase = 0;
+    if (valid) {
+        h.bw = __ldg(reinterpret_cast<const uint4*>(p.bitmap + tile * 128) + lane);
+        h.toff = __ldg(p.tile_off + tile);
+        const int qd = lane >> 3;
+        h.qbase = qd ? (int)__ldg(p.quarter_off + 3 * tile + qd - 1) : 0;
+    }
+    return h;
+}
+
+// popcounts -> 8-lane prefix (the three stored counts give the quarter bases)
+// -> this lane's position in the tile's sign stream -> its sign words.
+__device__ __forceinline__ TileSigns load_signs(const SpmmParams& p, const TileHead& h, bool valid, int lane) {
+    TileSigns sg;
+    const int c0 = __popc(h.bw.x), c1 = __popc(h.bw.y), c2 = __popc(h.bw.z), c3 = __popc(h.bw.w);
+    const int tot = c0 + c1 + c2 + c3;
+    int incl = tot;
 #pragma unroll
     for (int d = 1; d < 8; d <<= 1) {
         const int t = __shfl_up_sync(0xffffffffu, incl, d, 8);
         if ((lane & 7) >= d) incl += t;
     }
-    const int qd = lane >> 3;
-    const int qbase = qd ? (int)qoff_s[3 * i + qd - 1] : 0;
-    h.pos = toff_s[i] - w_first * 32 + qbase + incl - tot;
-    return h;
+    int pos = h.toff + h.qbase + incl - tot;
+    sg.pos = pos;
+    const int cn[4] = {c0, c1, c2, c3};
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const uint32_t* sw = p.signs + (pos >> 5);
+        sg.lo[r] = valid ? __ldg(sw) : 0u;
+        sg.hi[r] = valid ? __ldg(sw + 1) : 0u;
+        pos += cn[r];
+    }
+    return sg;
 }
 
 // One bitmap word (32 weights: rows g and g+8 of one 16-row group, 16 k) and
@@ -174,9 +191,63 @@ __device__ __forceinline__ void decode_word(uint32_t bmw, uint32_t sgn, uint32_t
     }
 }
 
-__device__ __forceinline__ uint32_t sign_window(uint32_t sg_base, int pos) {
-    const uint32_t sw = sg_base + (uint32_t)(pos >> 5) * 4u;
-    return __funnelshift_r(lds32(sw), lds32(sw + 4), pos & 31);
+// Entry of the second table, used for the upper nibble of a byte of bitmap:
+// index bits 0-3 = the four sign bits just BELOW the end of the byte's sign
+// run, bits 4-7 = the bitmap nibble.  The nibble's c non-zeros own the top c
+// of those four bits, in ascending order.
+__device__ __forceinline__ uint32_t lut_entry_upper(uint32_t e) {
+    const uint32_t x4 = e & 15u, nib = e >> 4;
+    const uint32_t c = __popc(nib);
+    uint32_t v = 0, r = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        if ((nib >> j) & 1u) {
+            v |= (((x4 >> (4 - c + r)) & 1u) ? 0xFFu : 0x01u) << (8 * j);
+            ++r;
+        }
+    return v;
+}
+
+// Same result as decode_word with 40 % fewer integer instructions, using two
+// tables.  Per byte of bitmap (two nibbles) ONE shift positions both nibbles
+// (lower at address bits 7-10, upper at 11-14) and per byte boundary ONE
+// funnel shift positions both neighbouring sign windows: with the window
+// pre-shifted by 11, shifting right by the number of non-zeros before the
+// boundary puts the four sign bits above it at bits 11-14 (they belong to the
+// lower nibble of the next byte, table `lut_lo`) and the four bits below it at
+// bits 7-10 (they end the sign run of the upper nibble of the previous byte,
+// table `lut_hi`, whose entries take their signs from the top of that field).
+__device__ __forceinline__ void decode_word2(uint32_t bmw, uint32_t sgn, int total, uint32_t lut_lo, uint32_t lut_hi,
+                                             uint32_t (&a)[8]) {
+    const uint32_t t1 = bmw - ((bmw >> 1) & 0x55555555u);
+    const uint32_t y = (t1 & 0x33333333u) + ((t1 >> 2) & 0x33333333u);  // popcount of each nibble
+    const uint32_t z = (y + (y >> 4)) & 0x0F0F0F0Fu;                    // popcount of each byte
+    const uint32_t pb = z * 0x01010100u;                                // byte b: non-zeros before byte b
+    const uint32_t glo = sgn << 11, ghi = sgn >> 21;
+    uint32_t yb[5];
+    yb[0] = glo;
+#pragma unroll
+    for (int b = 1; b < 4; ++b) yb[b] = __funnelshift_r(glo, ghi, pb >> (8 * b));   // shift amount is taken mod 32
+    yb[4] = __funnelshift_rc(glo, ghi, (uint32_t)total);   // total may be 32: clamp form, not wrap
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        const uint32_t bs = b == 0 ? (bmw << 7) : (bmw >> (8 * b - 7));  // nibble 2b at bits 7-10, nibble 2b+1 at 11-14
+        a[2 * b] = lds32((bs & 0x780u) | ((yb[b] & 0x7800u) | lut_lo));
+        a[2 * b + 1] = lds32((bs & 0x7800u) | ((yb[b + 1] & 0x780u) | lut_hi));
+    }
+}
+
+// Decode one tile (four bitmap words) into 4 x 8 A-fragment registers.
+__device__ __forceinline__ void decode_tile(const TileHead& h, const TileSigns& sg, uint32_t lut_lo, uint32_t lut_hi,
+                                            uint32_t (&a)[4][8]) {
+    const uint32_t w[4] = {h.bw.x, h.bw.y, h.bw.z, h.bw.w};
+    int pos = sg.pos;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int c = __popc(w[r]);
+        decode_word2(w[r], __funnelshift_r(sg.lo[r], sg.hi[r], (uint32_t)pos), c, lut_lo, lut_hi, a[r]);
+        pos += c;
+    }
 }
 
 template <int MT>
@@ -196,13 +267,10 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const Spm
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t dyn = (smem_u32(smem) + 127u) & ~127u;
     const uint32_t lut_base = (dyn + (uint32_t)kLutBytes - 1u) & ~((uint32_t)kLutBytes - 1u);
-    const uint32_t sbase = (lut_base - dyn >= (uint32_t)L::rest) ? dyn : lut_base + kLutBytes;  // "rest" region
+    const uint32_t sbase = (lut_base - dyn >= (uint32_t)L::rest) ? dyn : lut_base + kLut2Bytes;  // "rest" region
     uint8_t* rest = smem + (sbase - smem_u32(smem));
     int* red = reinterpret_cast<int*>(rest + L::red);
-    int* toff_s = reinterpret_cast<int*>(rest + L::toff);
-    uint16_t* qoff_s = reinterpret_cast<uint16_t*>(rest + L::qoff);
     float* scl_s = reinterpret_cast<float*>(rest + L::scl);
-    const uint32_t bar = sbase + L::bar;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int g = lane >> 2, q = lane & 3;
@@ -212,47 +280,31 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const Spm
     const int mrows = min(p.M - m0, MT * 8);
     const int KT = p.K >> 6;
     const int kt0 = (int)(((long long)KT * rank) / S), kt1 = (int)(((long long)KT * (rank + 1)) / S);
+    const long long tile0 = (long long)rt * KT;
 
     phase_mark(0);
     // Let the next kernel in the stream start its own weight prefetch now
     // (programmatic dependent launch; a no-op for ordinary launches).
     griddep_launch_dependents();
 
-    // ---- prologue: everything here touches only immutable weight data, so it
-    // may run while the previous kernel of the stream is still executing.
-    const int n0 = min(kChunkTiles, kt1 - kt0);
-    const long long tbase0 = (long long)rt * KT + kt0;
-    if (tid == 0) {
-        mbar_init(bar, 1);
-        mbar_fence_init();
-        mbar_expect_tx(bar, (uint32_t)(n0 * 512));
-        bulk_g2s(sbase + L::bm, p.bitmap + tbase0 * 128, (uint32_t)(n0 * 512), bar);
-    }
-    int toff_v = 0, qoff_v = 0;
-    if (tid <= n0) toff_v = p.tile_off[tbase0 + tid];
-    if (tid < 3 * n0) qoff_v = p.quarter_off[3 * tbase0 + tid];
-    // lookup table: the 256 entries once, then 32 copies (lane l reads bank l)
-    for (int e = tid; e < 256; e += blockDim.x) reinterpret_cast<uint32_t*>(rest + L::lut1)[e] = lut_entry(e);
+    // ---- prologue: everything up to the dependency wait touches only
+    // immutable weight data, so it may overlap the previous kernel.
+    // First loads of this warp's pipeline (tiles kt0+warp, +nwarps, ...):
+    int kt = kt0 + warp;
+    TileHead h_cur = load_head(p, tile0 + kt, kt < kt1, lane);
+    TileHead h_nxt = load_head(p, tile0 + kt + nwarps, kt + nwarps < kt1, lane);
+    // lookup tables: the 2 x 256 entries once, then 32 copies (lane l reads bank l)
+    for (int e = tid; e < 512; e += blockDim.x)
+        reinterpret_cast<uint32_t*>(rest + L::lut1)[e] = e < 256 ? lut_entry(e) : lut_entry_upper(e - 256);
     for (int i = tid; i < MT * 8 * kRedStride; i += blockDim.x) red[i] = 0;
-    if (tid <= n0) toff_s[tid] = toff_v;
-    if (tid < 3 * n0) qoff_s[tid] = (uint16_t)qoff_v;
     __syncthreads();
-    int w_first = (toff_s[0] >> 5) & ~3;  // first sign word of the chunk, rounded down to 16 bytes
-    if (tid == 0) {
-        const int w_end = ((toff_s[n0] >> 5) + 3) & ~3;
-        const uint32_t bytes = (uint32_t)(w_end - w_first) * 4u;
-        if (bytes) {
-            mbar_expect_tx(bar, bytes);
-            bulk_g2s(sbase + L::sg, p.signs + w_first, bytes, bar);
-        }
-        mbar_arrive(bar);
-    }
-    for (int i = tid; i < 256 * 8; i += blockDim.x) {
+    for (int i = tid; i < 512 * 8; i += blockDim.x) {
         const uint32_t v = reinterpret_cast<const uint32_t*>(rest + L::lut1)[i >> 3];
         sts128(lut_base + i * 16, make_uint4(v, v, v, v));
     }
+    TileSigns s_cur = load_signs(p, h_cur, kt < kt1, lane);
     __syncthreads();
-    cluster_arrive();  // this CTA's reduction buffer is zeroed
+    if (S > 1) cluster_arrive();  // this CTA's reduction buffer is zeroed
     phase_mark(1);
 
     int acc[4][MT][4];
@@ -263,36 +315,14 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const Spm
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[r][mt][c] = 0;
 
-    const uint32_t lut_lane = lut_base | (uint32_t)(lane * 4);
-    // One warp polls the copy barrier; the others sleep at the CTA barrier
-    // instead of spending issue slots on polling.
-    volatile int* ok_flag = reinterpret_cast<volatile int*>(rest + L::flag);
-    uint32_t phase = 0;
-    if (warp == 0) {
-        const bool arrived = mbar_wait_bounded(bar, phase);
-        if (lane == 0) *ok_flag = arrived;
-    }
-    __syncthreads();
-    bool ok = *ok_flag != 0;
-    phase ^= 1u;
-    phase_mark(2);
+    const uint32_t lut_lo = lut_base | (uint32_t)(lane * 4), lut_hi = lut_lo + kLutBytes;
 
-    // ---- decode this warp's first tile(s) into registers before the wait
-    uint32_t pre[kPreTiles][4][8];
-    if (ok) {
-#pragma unroll
-        for (int tp = 0; tp < kPreTiles; ++tp) {
-            const int i = warp + tp * nwarps;
-            if (i < n0) {
-                TileHead h = tile_head(sbase + L::bm + i * 512, toff_s, qoff_s, i, w_first, lane);
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    decode_word(h.w[r], sign_window(sbase + L::sg, h.pos), lut_lane, pre[tp][r]);
-                    h.pos += h.cnt[r];
-                }
-            }
-        }
-    }
+    // ---- decode this warp's first tile into registers before the wait
+    uint32_t pre[4][8];
+    const bool have_first = kt < kt1;
+    if (have_first) decode_tile(h_cur, s_cur, lut_lo, lut_hi, pre);
+    TileSigns s_nxt = load_signs(p, h_nxt, kt + nwarps < kt1, lane);
+    TileHead h_far = load_head(p, tile0 + kt + 2 * nwarps, kt + 2 * nwarps < kt1, lane);
     phase_mark(3);
 
     // ---- activations, scales and the output may belong to the previous kernel
@@ -301,76 +331,35 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const Spm
     if (tid < mrows && p.epilogue != EPI_RAW_I32) scl_s[tid] = __bfloat162float(p.s[m0 + tid]);
     if (tid >= 32 && tid < 36 && p.epilogue != EPI_RAW_I32) scl_s[MT * 8 + tid - 32] = __bfloat162float(p.ws[tid - 32]);
 
-    if (ok) {
+    if (have_first) {
+        uint4 bx[MT];
+        load_x_frags<MT>(bx, p.x, p.K, m0, mrows, kt, g, q);
 #pragma unroll
-        for (int tp = 0; tp < kPreTiles; ++tp) {
-            const int i = warp + tp * nwarps;
-            if (i < n0) {
-                uint4 bx[MT];
-                load_x_frags<MT>(bx, p.x, p.K, m0, mrows, kt0 + i, g, q);
+        for (int r = 0; r < 4; ++r)
 #pragma unroll
-                for (int r = 0; r < 4; ++r)
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        mma_s8_16x8x32(acc[r][mt], pre[tp][r][0], pre[tp][r][1], pre[tp][r][2], pre[tp][r][3],
-                                       bx[mt].x, bx[mt].y);
-                        mma_s8_16x8x32(acc[r][mt], pre[tp][r][4], pre[tp][r][5], pre[tp][r][6], pre[tp][r][7],
-                                       bx[mt].z, bx[mt].w);
-                    }
+            for (int mt = 0; mt < MT; ++mt) {
+                mma_s8_16x8x32(acc[r][mt], pre[r][0], pre[r][1], pre[r][2], pre[r][3], bx[mt].x, bx[mt].y);
+                mma_s8_16x8x32(acc[r][mt], pre[r][4], pre[r][5], pre[r][6], pre[r][7], bx[mt].z, bx[mt].w);
             }
-        }
     }
 
-    // ---- remaining tiles: streamed (decode + multiply), chunk by chunk
-    for (int c0 = kt0; c0 < kt1 && ok; c0 += kChunkTiles) {
-        const int n = min(kChunkTiles, kt1 - c0);
-        if (c0 != kt0) {
-            const long long tbase = (long long)rt * KT + c0;
-            __syncthreads();  // every warp is done with the previous chunk
-            if (tid == 0) {
-                mbar_expect_tx(bar, (uint32_t)(n * 512));
-                bulk_g2s(sbase + L::bm, p.bitmap + tbase * 128, (uint32_t)(n * 512), bar);
-            }
-            if (tid <= n) toff_s[tid] = p.tile_off[tbase + tid];
-            if (tid < 3 * n) qoff_s[tid] = p.quarter_off[3 * tbase + tid];
-            __syncthreads();
-            w_first = (toff_s[0] >> 5) & ~3;
-            if (tid == 0) {
-                const int w_end = ((toff_s[n] >> 5) + 3) & ~3;
-                const uint32_t bytes = (uint32_t)(w_end - w_first) * 4u;
-                if (bytes) {
-                    mbar_expect_tx(bar, bytes);
-                    bulk_g2s(sbase + L::sg, p.signs + w_first, bytes, bar);
-                }
-                mbar_arrive(bar);
-            }
-            if (warp == 0) {
-                const bool arrived = mbar_wait_bounded(bar, phase);
-                if (lane == 0) *ok_flag = arrived;
-            }
-            __syncthreads();
-            ok = *ok_flag != 0;
-            phase ^= 1u;
-            if (!ok) break;
-        }
-        for (int i = warp + (c0 == kt0 ? kPreTiles * nwarps : 0); i < n; i += nwarps) {
-            TileHead h = tile_head(sbase + L::bm + i * 512, toff_s, qoff_s, i, w_first, lane);
-            uint4 bx[MT];
-            load_x_frags<MT>(bx, p.x, p.K, m0, mrows, c0 + i, g, q);
+    // ---- remaining tiles of this warp: streamed through the register pipeline
+    for (kt += nwarps; kt < kt1; kt += nwarps) {
+        h_cur = h_nxt, s_cur = s_nxt, h_nxt = h_far;
+        uint4 bx[MT];
+        load_x_frags<MT>(bx, p.x, p.K, m0, mrows, kt, g, q);
+        s_nxt = load_signs(p, h_nxt, kt + nwarps < kt1, lane);
+        h_far = load_head(p, tile0 + kt + 2 * nwarps, kt + 2 * nwarps < kt1, lane);
+        uint32_t a[4][8];
+        decode_tile(h_cur, s_cur, lut_lo, lut_hi, a);
 #pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                uint32_t a[8];
-                decode_word(h.w[r], sign_window(sbase + L::sg, h.pos), lut_lane, a);
-                h.pos += h.cnt[r];
+        for (int r = 0; r < 4; ++r)
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    mma_s8_16x8x32(acc[r][mt], a[0], a[1], a[2], a[3], bx[mt].x, bx[mt].y);
-                    mma_s8_16x8x32(acc[r][mt], a[4], a[5], a[6], a[7], bx[mt].z, bx[mt].w);
-                }
+            for (int mt = 0; mt < MT; ++mt) {
+                mma_s8_16x8x32(acc[r][mt], a[r][0], a[r][1], a[r][2], a[r][3], bx[mt].x, bx[mt].y);
+                mma_s8_16x8x32(acc[r][mt], a[r][4], a[r][5], a[r][6], a[r][7], bx[mt].z, bx[mt].w);
             }
-        }
     }
-    if (!ok && tid == 0) atomicExch(p.status, ST_WAIT_TIMEOUT);
     phase_mark(5);
 
     // ---- combine: warps -> CTA buffer -> cluster rank 0
@@ -385,19 +374,21 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const Spm
             }
     __syncthreads();
     phase_mark(6);
-    cluster_wait();  // every CTA of the cluster has zeroed its buffer
-    phase_mark(7);
-    if (rank != 0) {
-        const uint32_t remote = map_to_rank(sbase + L::red, 0);
-        for (int i = tid; i < MT * 8 * kRedStride; i += blockDim.x) {
-            const int v = red[i];
-            if (v != 0) red_add_cluster(remote + i * 4, v);
+    if (S > 1) {
+        cluster_wait();  // every CTA of the cluster has zeroed its buffer
+        phase_mark(7);
+        if (rank != 0) {
+            const uint32_t remote = map_to_rank(sbase + L::red, 0);
+            for (int i = tid; i < MT * 8 * kRedStride; i += blockDim.x) {
+                const int v = red[i];
+                if (v != 0) red_add_cluster(remote + i * 4, v);
+            }
         }
+        cluster_arrive();
+        cluster_wait();  // all partial sums have landed in rank 0
+        phase_mark(8);
+        if (rank != 0) return;
     }
-    cluster_arrive();
-    cluster_wait();  // all partial sums have landed in rank 0
-    phase_mark(8);
-    if (rank != 0) return;
 
     // ---- epilogue (rank 0): scale and store
     const int N = p.N;

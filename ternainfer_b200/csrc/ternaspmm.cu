@@ -71,7 +71,7 @@ struct LaunchShape {
 
 // K split (= cluster size, at most 8) and warps per CTA.  Take the smallest
 // number of tiles per warp for which every CTA is resident at once (one wave:
-// `warp_slots` warps and at most 3 CTAs per SM at this kernel's register and
+// `warp_slots` warps and at most 2 CTAs per SM at this kernel's register and
 // shared-memory budget), and for that the smallest cluster.
 // TERNASPMM_CTAS_PER_SM_X10 > 0 overrides with "about that many CTAs per SM".
 static LaunchShape choose_shape(int RT, int KT, int token_blocks, int max_warps, int warp_slots) {
@@ -93,7 +93,7 @@ static LaunchShape choose_shape(int RT, int KT, int token_blocks, int max_warps,
             if (w > max_w) continue;
             if (w < 2) w = 2;
             int per_sm = warp_slots / w;
-            per_sm = per_sm > 3 ? 3 : per_sm;
+            per_sm = per_sm > 2 ? 2 : per_sm;
             if (rows * s <= (long long)sms * per_sm) return {s, w};
         }
     const int nt = (KT + max_s - 1) / max_s;   // more than one wave whatever we do
@@ -243,9 +243,9 @@ static void run_spmm(int8_t* x, uint64_t* bitmap, int* tile_off, uint16_t* quart
         p.splits = 1;
         e = M <= 64 ? launch_large_m<64>(p, stream) : (M <= 128 ? launch_large_m<128>(p, stream) : launch_large_m<256>(p, stream));
     } else if (M <= 8) {
-        e = launch_small_m<1, 16, 2>(p, 1, 32, stream);
+        e = launch_small_m<1, 14, 2>(p, 1, 28, stream);
     } else if (M <= 16) {
-        e = launch_small_m<2, 12, 2>(p, 1, 24, stream);
+        e = launch_small_m<2, 10, 2>(p, 1, 20, stream);
     } else {
         e = launch_small_m<4, 8, 2>(p, (M + 31) / 32, 16, stream);
     }
