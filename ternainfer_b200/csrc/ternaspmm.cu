@@ -96,8 +96,8 @@ static LaunchShape choose_shape(int RT, int KT, int token_blocks, int max_warps,
             per_sm = per_sm > 2 ? 2 : per_sm;
             if (rows * s <= (long long)sms * per_sm) return {s, w};
         }
-    const int nt = (KT + max_s - 1) / max_s;   // more than one wave whatever we do
-    return {max_s, nt < 2 ? 2 : (nt > max_w ? max_w : nt)};
+    // more than one wave whatever we do: no K split, full CTAs
+    return {1, KT < 2 ? 2 : (KT > max_w ? max_w : KT)};
 }
 
 template <int MT, int MAXW, int MINB>
@@ -239,7 +239,12 @@ static void run_spmm(int8_t* x, uint64_t* bitmap, int* tile_off, uint16_t* quart
         return;
     }
     cudaError_t e;
-    if (M >= tuning().large_min_m) {
+    // Kernel choice.  Up to 32 tokens: the small-batch kernel.  Above that the
+    // tcgen05 kernel, except for narrow weights at up to 128 tokens, where its
+    // 128-row tiles would occupy less than half of the SMs and the small-batch
+    // kernel run over blocks of 32 tokens is faster.
+    const bool narrow = M <= 128 && (N + 127) / 128 < device_sm_count() / 2;
+    if (M >= tuning().large_min_m && !(narrow && tuning().large_min_m == 33)) {
         p.splits = 1;
         e = M <= 64 ? launch_large_m<64>(p, stream) : (M <= 128 ? launch_large_m<128>(p, stream) : launch_large_m<256>(p, stream));
     } else if (M <= 8) {
