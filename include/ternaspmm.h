@@ -130,6 +130,29 @@ void ternaspmm_linear_segments(int8_t* x, uint64_t* bitmap, int* tile_offsets,
                                int ws_num, int M, int N, int K, int seg1, int seg2, int seg3,
                                int prefill_form, ternaspmm_stream_t stream);
 
+/* bitlinear_TernaSpMM with the residual add of the decoder block fused into
+ * the epilogue: out = bf16(residual + bf16(linear(x))), residual bf16 [M][N]
+ * (may alias out; null = plain linear). */
+void bitlinear_TernaSpMM_residual(int8_t* x, uint64_t* bitmap, int* tile_offsets,
+                                  uint16_t* quarter_offsets, uint32_t* sign_words,
+                                  ternaspmm_bf16* out, ternaspmm_bf16* s, ternaspmm_bf16* ws,
+                                  int ws_num, int M, int N, int K, ternaspmm_bf16* residual,
+                                  ternaspmm_stream_t stream);
+
+/* Fused front-end of a ternary linear: y = RMSNorm(x) * norm_weight (fp32 sum
+ * of squares, bf16 result), then the per-token absmax int8 quantiser of
+ * model.py:120-123: s = 127 / clamp(max|y|, 1e-5), q = clamp(round(y*s)).
+ * One kernel instead of the reference's RMSNorm + Triton quantiser chain.
+ * x bf16 [M][K], norm_weight bf16 [K], q int8 [M][K], s_out bf16 [M];
+ * K a multiple of 16, at most 57344; x, norm_weight, q 16-byte aligned. */
+void ternaspmm_rmsnorm_quant(ternaspmm_bf16* x, ternaspmm_bf16* norm_weight, float eps, int M, int K,
+                             int8_t* q, ternaspmm_bf16* s_out, ternaspmm_stream_t stream);
+
+/* The same for the input of the down projection (model.py:277-282): x13 bf16
+ * [M][2K] holds [x1 | x3]; y = RMSNorm(relu(x1)^2 * x3) * norm_weight. */
+void ternaspmm_relu2_gate_rmsnorm_quant(ternaspmm_bf16* x13, ternaspmm_bf16* norm_weight, float eps, int M,
+                                        int K, int8_t* q, ternaspmm_bf16* s_out, ternaspmm_stream_t stream);
+
 /* Host packer from int8 ternary [N][K] into caller-provided arrays
  * (bitmap N*K/64, tile_offsets tiles+1, quarter_offsets 3*tiles, sign_words
  * at least N*K/32 + 4 words, zero-filled by the call).  Returns the number of

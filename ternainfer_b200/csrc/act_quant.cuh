@@ -1,0 +1,117 @@
+// Fused activation front-ends of the ternary linears for sm_100a: the work the
+// reference does between two TernaSpMM calls with a chain of small library
+// kernels (xformers RMSNorm, the Triton-compiled `quant_input`, `squared_relu`;
+// model.py:120-123, 235-243, 277-282, 323-335 of Gu-J/TernaInfer) as ONE kernel
+// per linear input:
+//   norm_quant       x -> RMSNorm(x) * w -> per-token absmax int8 + scale
+//   gated_norm_quant [x1 | x3] -> relu(x1)^2 * x3 -> RMSNorm * w -> int8 + scale
+// One CTA per token row; the row is staged once in shared memory as bf16, so
+// HBM traffic is one read of the activations and one write of int8 + scale.
+// Rounding points follow the eager PyTorch evaluation of the same expressions
+// (bf16 after the norm, bf16(1/amax) * 127 for the scale, bf16(x*s) before the
+// round-half-even), the sum of squares is accumulated in fp32.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx_sm100.cuh"
+
+namespace tsp {
+
+constexpr int kActThreads = 256;
+
+__device__ __forceinline__ float bf16_round_f(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+__device__ __forceinline__ float block_reduce(float v, float* scratch, bool is_max) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        const float o = __shfl_xor_sync(0xffffffffu, v, d);
+        v = is_max ? fmaxf(v, o) : v + o;
+    }
+    __syncthreads();   // scratch may still be read from the previous reduction
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = scratch[0];
+    for (int i = 1; i < kActThreads / 32; ++i) r = is_max ? fmaxf(r, scratch[i]) : r + scratch[i];
+    return r;
+}
+
+// x: [M][ld] bf16 (GATED: the row holds [x1 (K) | x3 (K)], ld = 2K), w: [K] bf16 norm weight,
+// q: [M][K] int8, s_out: [M] bf16.  Dynamic shared memory: K bf16.
+template <bool GATED>
+__global__ void __launch_bounds__(kActThreads) norm_quant_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                  const __nv_bfloat16* __restrict__ w, float eps,
+                                                                  int K, int8_t* __restrict__ q,
+                                                                  __nv_bfloat16* __restrict__ s_out) {
+    extern __shared__ __align__(16) uint8_t act_smem[];
+    __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(act_smem);
+    __shared__ float scratch[kActThreads / 32];
+    griddep_launch_dependents();
+    griddep_wait();   // the activations come from the previous kernel
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const __nv_bfloat16* xr = x + (size_t)t * (GATED ? 2 * K : K);
+
+    // pass 1: stage the row (after the gate, if any) and its sum of squares
+    float ss = 0.f;
+    for (int k0 = tid * 8; k0 < K; k0 += kActThreads * 8) {
+        const uint4 a = *reinterpret_cast<const uint4*>(xr + k0);
+        const __nv_bfloat16* av = reinterpret_cast<const __nv_bfloat16*>(&a);
+        __align__(16) __nv_bfloat16 v[8];
+        if (GATED) {
+            const uint4 b = *reinterpret_cast<const uint4*>(xr + K + k0);
+            const __nv_bfloat16* bv = reinterpret_cast<const __nv_bfloat16*>(&b);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float r = fmaxf(__bfloat162float(av[i]), 0.f);
+                const float sq = bf16_round_f(r * r);                       // relu(x1) ** 2, bf16
+                v[i] = __float2bfloat16_rn(sq * __bfloat162float(bv[i]));   // * x3, bf16
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = av[i];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float f = __bfloat162float(v[i]);
+            ss += f * f;
+        }
+        *reinterpret_cast<uint4*>(row + k0) = *reinterpret_cast<const uint4*>(v);
+    }
+    ss = block_reduce(ss, scratch, false);
+    const float rstd = rsqrtf(ss / (float)K + eps);
+
+    // pass 2: normalise, apply the weight, round to bf16, absmax
+    float amax = 0.f;
+    for (int k0 = tid * 8; k0 < K; k0 += kActThreads * 8) {
+        uint4 a = *reinterpret_cast<const uint4*>(row + k0);
+        const uint4 wv = *reinterpret_cast<const uint4*>(w + k0);
+        __nv_bfloat16* av = reinterpret_cast<__nv_bfloat16*>(&a);
+        const __nv_bfloat16* ww = reinterpret_cast<const __nv_bfloat16*>(&wv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float y = (__bfloat162float(av[i]) * rstd) * __bfloat162float(ww[i]);
+            av[i] = __float2bfloat16_rn(y);
+            amax = fmaxf(amax, fabsf(__bfloat162float(av[i])));
+        }
+        *reinterpret_cast<uint4*>(row + k0) = a;
+    }
+    amax = block_reduce(amax, scratch, true);
+    amax = bf16_round_f(fmaxf(amax, 1e-5f));
+    const float s = bf16_round_f(bf16_round_f(1.0f / amax) * 127.0f);   // 127 / amax as reciprocal * 127, in bf16
+    if (tid == 0) s_out[t] = __float2bfloat16_rn(s);
+
+    // pass 3: quantise
+    for (int k0 = tid * 16; k0 < K; k0 += kActThreads * 16) {
+        __align__(16) int8_t o[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float p = bf16_round_f(__bfloat162float(row[k0 + i]) * s);
+            o[i] = (int8_t)fminf(fmaxf(rintf(p), -128.f), 127.f);
+        }
+        *reinterpret_cast<uint4*>(q + (size_t)t * K + k0) = *reinterpret_cast<const uint4*>(o);
+    }
+}
+
+}  // namespace tsp

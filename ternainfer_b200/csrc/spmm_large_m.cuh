@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(kLgThreads, 1)
                     if (n_ok && t < M) {
                         const long long o = (long long)t * N + n;
                         if (p.epilogue == EPI_RAW_I32) reinterpret_cast<int*>(p.out)[o] = v[j];
-                        else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = scale_epilogue(v[j], s_s[c0 + j], ws_el, p.epilogue);
+                        else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = add_residual(scale_epilogue(v[j], s_s[c0 + j], ws_el, p.epilogue), p.residual, o);
                     }
                 }
             }

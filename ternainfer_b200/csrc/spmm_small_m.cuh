@@ -37,6 +37,7 @@ struct SpmmParams {
     void* out;                   // bf16 [M][N] or int32 [M][N]
     const __nv_bfloat16* s;      // [M]
     const __nv_bfloat16* ws;     // [4]
+    const __nv_bfloat16* residual;  // optional bf16 [M][N] added to the rounded result (residual stream), or null
     int ws_num, M, N, K, epilogue, splits;
     int seg_b[3];   // first output column of scale segments 1, 2, 3 (INT_MAX when absent)
     int seg_gran;   // 1, or the reference's granularity: 8 (decode form) / 128 (prefill form)
@@ -117,6 +118,12 @@ __device__ __forceinline__ __nv_bfloat16 scale_epilogue(int acc, float s_el, flo
         v = __fmul_rn(__fdiv_rn(__int2float_rn(acc), s_el), ws_el);
     }
     return __float2bfloat16_rn(v);
+}
+
+// out = linear(x) or, with a residual, bf16(residual + bf16(linear(x))): the
+// two roundings of `h = x + wo(...)` in model.py:323-335 of the reference.
+__device__ __forceinline__ __nv_bfloat16 add_residual(__nv_bfloat16 v, const __nv_bfloat16* residual, long long o) {
+    return residual ? __float2bfloat16_rn(__bfloat162float(residual[o]) + __bfloat162float(v)) : v;
 }
 
 // One 64x64 tile as a warp sees it while it is in flight: the lane's four
@@ -402,7 +409,7 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const Spm
         } else {
             const float s_el = scl_s[t];
             const float ws_el = scl_s[MT * 8 + ws_group(n, p)];
-            reinterpret_cast<__nv_bfloat16*>(p.out)[o] = scale_epilogue(v, s_el, ws_el, p.epilogue);
+            reinterpret_cast<__nv_bfloat16*>(p.out)[o] = add_residual(scale_epilogue(v, s_el, ws_el, p.epilogue), p.residual, o);
         }
     }
     phase_mark(9);

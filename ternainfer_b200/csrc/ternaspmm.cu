@@ -10,6 +10,7 @@
 #include <limits.h>
 #include <stdlib.h>
 
+#include "act_quant.cuh"
 #include "spmm_large_m.cuh"
 #include "spmm_small_m.cuh"
 
@@ -190,7 +191,7 @@ static cudaError_t launch_large_m(const SpmmParams& p, cudaStream_t stream) {
 
 static void run_spmm(int8_t* x, uint64_t* bitmap, int* tile_off, uint16_t* quarter_off, uint32_t* signs, void* out,
                      __nv_bfloat16* s, __nv_bfloat16* ws, int ws_num, int M, int N, int K, int epilogue,
-                     cudaStream_t stream, const int* seg_bounds = nullptr) {
+                     cudaStream_t stream, const int* seg_bounds = nullptr, const __nv_bfloat16* residual = nullptr) {
     t_host_status = ST_OK;
     if (M < 1 || N < 64 || K < 64 || (N % 64) || (K % 64) ||
         (epilogue != EPI_RAW_I32 && (ws_num < 1 || ws_num > 4))) {
@@ -215,6 +216,7 @@ static void run_spmm(int8_t* x, uint64_t* bitmap, int* tile_off, uint16_t* quart
     p.out = out;
     p.s = s;
     p.ws = ws;
+    p.residual = residual;
     p.ws_num = ws_num;
     p.M = M;
     p.N = N;
@@ -312,6 +314,15 @@ extern "C" void bitlinear_TernaSpMM_prefill(int8_t* x, uint64_t* bitmap, int* ti
     checkLastCudaError(__LINE__);
 }
 
+extern "C" void bitlinear_TernaSpMM_residual(int8_t* x, uint64_t* bitmap, int* tile_offsets,
+                                            uint16_t* quarter_offsets, uint32_t* sign_words, __nv_bfloat16* out,
+                                            __nv_bfloat16* s, __nv_bfloat16* ws, int ws_num, int M, int N, int K,
+                                            __nv_bfloat16* residual, cudaStream_t stream) {
+    run_spmm(x, bitmap, tile_offsets, quarter_offsets, sign_words, out, s, ws, ws_num, M, N, K,
+             M <= 64 ? EPI_DECODE : EPI_PREFILL, stream, nullptr, residual);
+    checkLastCudaError(__LINE__);
+}
+
 extern "C" void ternaspmm_accumulate_i32(int8_t* x, uint64_t* bitmap, int* tile_offsets, uint16_t* quarter_offsets,
                                          uint32_t* sign_words, int32_t* out, int M, int N, int K,
                                          cudaStream_t stream) {
@@ -327,6 +338,55 @@ extern "C" void ternaspmm_linear_segments(int8_t* x, uint64_t* bitmap, int* tile
     const int b[3] = {seg1, seg2, seg3};
     const int epi = prefill_form < 0 ? (M <= 64 ? EPI_DECODE : EPI_PREFILL) : (prefill_form ? EPI_PREFILL : EPI_DECODE);
     run_spmm(x, bitmap, tile_offsets, quarter_offsets, sign_words, out, s, ws, ws_num, M, N, K, epi, stream, b);
+    checkLastCudaError(__LINE__);
+}
+
+static void run_norm_quant(bool gated, __nv_bfloat16* x, __nv_bfloat16* w, float eps, int M, int K, int8_t* q,
+                           __nv_bfloat16* s_out, cudaStream_t stream) {
+    t_host_status = ST_OK;
+    if (M < 1 || K < 16 || (K % 16) || K > 56 * 1024) {
+        fprintf(stderr, "ternaspmm: norm_quant needs M>=1 and K a multiple of 16 up to 57344 (got M=%d K=%d)\n", M, K);
+        t_host_status = ST_BAD_SHAPE;
+        return;
+    }
+    if (!x || !w || !q || !s_out || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
+        (reinterpret_cast<uintptr_t>(q) & 15)) {
+        fprintf(stderr, "ternaspmm: norm_quant: null or misaligned pointer\n");
+        t_host_status = ST_BAD_POINTER;
+        return;
+    }
+    static bool attr_done[64][2] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    auto kern = gated ? norm_quant_kernel<true> : norm_quant_kernel<false>;
+    if (!attr_done[dev][gated]) {
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 56 * 1024);
+        attr_done[dev][gated] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(M, 1, 1);
+    cfg.blockDim = dim3(kActThreads, 1, 1);
+    cfg.dynamicSmemBytes = (size_t)K * 2;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tuning().pdl ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, kern, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, eps, K, q, s_out) != cudaSuccess)
+        t_host_status = ST_LAUNCH;
+}
+
+extern "C" void ternaspmm_rmsnorm_quant(__nv_bfloat16* x, __nv_bfloat16* norm_weight, float eps, int M, int K,
+                                       int8_t* q, __nv_bfloat16* s_out, cudaStream_t stream) {
+    run_norm_quant(false, x, norm_weight, eps, M, K, q, s_out, stream);
+    checkLastCudaError(__LINE__);
+}
+
+extern "C" void ternaspmm_relu2_gate_rmsnorm_quant(__nv_bfloat16* x13, __nv_bfloat16* norm_weight, float eps, int M,
+                                                  int K, int8_t* q, __nv_bfloat16* s_out, cudaStream_t stream) {
+    run_norm_quant(true, x13, norm_weight, eps, M, K, q, s_out, stream);
     checkLastCudaError(__LINE__);
 }
 

@@ -109,8 +109,9 @@ def main():
     ap.add_argument("--gen_length", type=int, default=128)
     ap.add_argument("--no_cuda_graph", action="store_true")
     ap.add_argument("--seed", type=int, default=1234)
+    ap.add_argument("--fused_glue", action="store_true", help="fused norm+quantiser kernels, residual add in the epilogue")
     a = ap.parse_args()
-    margs = ModelArgs(n_layers=a.layers)
+    margs = ModelArgs(n_layers=a.layers, fused_glue=a.fused_glue)
     model, _ = build_random_model(margs, a.prompt_length + a.gen_length, a.seed)
     gen = FastGen(model, GenArgs(a.gen_length, a.bsz, a.prompt_length, not a.no_cuda_graph))
     g = torch.Generator(device="cuda").manual_seed(a.seed + 1)

@@ -62,6 +62,12 @@ def load_library() -> ctypes.CDLL:
     lib.ternaspmm_accumulate_i32.restype = None
     lib.ternaspmm_linear_segments.argtypes = [_P] * 8 + [_I] * 8 + [_P]
     lib.ternaspmm_linear_segments.restype = None
+    for name in ("ternaspmm_rmsnorm_quant", "ternaspmm_relu2_gate_rmsnorm_quant"):
+        fn = getattr(lib, name)
+        fn.argtypes = [_P, _P, ctypes.c_float, _I, _I, _P, _P, _P]
+        fn.restype = None
+    lib.bitlinear_TernaSpMM_residual.argtypes = [_P] * 8 + [_I] * 4 + [_P, _P]
+    lib.bitlinear_TernaSpMM_residual.restype = None
     lib.ternaspmm_pack_i8.argtypes = [_P, _I, _I, _P, _P, _P, _P]
     lib.ternaspmm_pack_i8.restype = ctypes.c_longlong
     lib.ternaspmm_unpack_i8.argtypes = [_P, _P, _P, _I, _I, _P]
@@ -75,6 +81,6 @@ def load_library() -> ctypes.CDLL:
 EXPORTED_SYMBOLS = (
     "bitlinear_TernaSpMM", "bitlinear_TernaSpMM_decode", "bitlinear_TernaSpMM_prefill",
     "bitlinear_TernaSpMM_benchmark", "checkLastCudaError", "reorder_WT_h", "convert_reorderd",
-    "gpu_sleep", "ternaspmm_last_status", "ternaspmm_accumulate_i32", "ternaspmm_linear_segments", "ternaspmm_pack_i8",
+    "gpu_sleep", "ternaspmm_last_status", "ternaspmm_accumulate_i32", "ternaspmm_linear_segments", "bitlinear_TernaSpMM_residual", "ternaspmm_rmsnorm_quant", "ternaspmm_relu2_gate_rmsnorm_quant", "ternaspmm_pack_i8",
     "ternaspmm_unpack_i8", "ternaspmm_transcode_reference_layout",
 )

@@ -44,8 +44,26 @@ _ENTRY = {"auto": "bitlinear_TernaSpMM", "decode": "bitlinear_TernaSpMM_decode",
           "prefill": "bitlinear_TernaSpMM_prefill"}
 
 
+def rmsnorm_quant(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, gated: bool = False):
+    """One fused kernel for RMSNorm(x) * weight followed by ``quant_input``
+    (``gated``: x holds [x1 | x3] and the normalised value is relu(x1)^2 * x3).
+    bf16 [..., K or 2K] -> (int8 [..., K], bf16 scale [..., 1])."""
+    if not x.is_cuda:
+        raise RuntimeError("rmsnorm_quant needs CUDA tensors: the B200 library has no CPU path")
+    lib = load_library()
+    K = norm_weight.shape[0]
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    M = x2.shape[0]
+    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    s = torch.empty((M, 1), dtype=torch.bfloat16, device=x.device)
+    fn = lib.ternaspmm_relu2_gate_rmsnorm_quant if gated else lib.ternaspmm_rmsnorm_quant
+    fn(x2.data_ptr(), norm_weight.data_ptr(), float(eps), M, K, q.data_ptr(), s.data_ptr(),
+       torch.cuda.current_stream().cuda_stream)
+    return q.reshape(*x.shape[:-1], K), s.reshape(*x.shape[:-1], 1)
+
+
 def TernaInfer_linear(input, compressed_val, TileOffsets_global, TileOffsets_median, bitmap,
-                      workspace, s, ws, ws_num, out_features, mode: str = "auto"):
+                      workspace, s, ws, ws_num, out_features, mode: str = "auto", residual=None):
     """out = TernaSpMM(input_int8, packed weight) as bf16 (model.py:45-92).
     ``input`` is int8 [..., K] on the GPU, ``s`` its per-token bf16 scale,
     ``ws`` the 4-slot bf16 weight scale with ``ws_num`` non-zero slots."""
@@ -64,6 +82,14 @@ def TernaInfer_linear(input, compressed_val, TileOffsets_global, TileOffsets_med
     s = s.contiguous()
     ret = torch.empty((M, out_features), dtype=torch.bfloat16, device=input.device)
     stream = torch.cuda.current_stream()
+    if residual is not None:
+        res = residual.reshape(M, out_features)
+        assert mode == "auto" and res.is_contiguous() and res.dtype == torch.bfloat16
+        lib.bitlinear_TernaSpMM_residual(x2.data_ptr(), bitmap.data_ptr(), TileOffsets_global.data_ptr(),
+                                         TileOffsets_median.data_ptr(), compressed_val.data_ptr(), ret.data_ptr(),
+                                         s.data_ptr(), ws.data_ptr(), ws_num, M, out_features, K, res.data_ptr(),
+                                         stream.cuda_stream)
+        return ret.reshape(*out_shape)
     getattr(lib, _ENTRY[mode])(
         ctypes.c_void_p(x2.data_ptr()),
         ctypes.c_void_p(bitmap.data_ptr()),
@@ -103,6 +129,13 @@ class SpBitLinear(nn.Module):
         self.ws_num = int((ws != 0).sum().item())
 
     quant_input = staticmethod(quant_input)
+
+    def forward_quantized(self, input_q, s, residual=None):
+        """Already quantised input (int8 + per-token scale), optional fused residual add."""
+        return TernaInfer_linear(
+            input_q,
+            self.weight_compressed_val, self.weight_TileOffsets_global, self.weight_TileOffsets_median,
+            self.weight_bitmap, None, s, self.weight_scale, self.ws_num, self.out_features, residual=residual)
 
     def forward(self, input):
         input, s = quant_input(input)

@@ -20,7 +20,7 @@ import torch
 from torch import nn
 from torch.nn import functional as F
 
-from .linear import SpBitLinear, quant_input
+from .linear import SpBitLinear, quant_input, rmsnorm_quant
 
 
 @dataclass
@@ -34,6 +34,7 @@ class ModelArgs:
     norm_eps: float = 1e-5
     rope_theta: float = 500000.0
     use_kernel: bool = True
+    fused_glue: bool = False     # fused norm+quantiser kernels and residual add in the linear epilogue
 
     @property
     def head_dim(self) -> int:
@@ -102,10 +103,11 @@ class Attention(nn.Module):
             with torch.no_grad():
                 self.attn_sub_norm.weight.copy_(dic[prefix + ".attn_sub_norm.weight"])
 
-    def forward(self, x, cache: LayerCache, pos, cos, sin, mask):
-        B, T, _ = x.shape
+    def forward(self, x, cache: LayerCache, pos, cos, sin, mask, fused=None):
+        """``fused`` = (x_q, s, residual, eps): quantised input of wqkv and the residual for wo's epilogue."""
+        B, T = x.shape[0], x.shape[1]
         H, Hkv, D = self.n_heads, self.n_kv_heads, self.head_dim
-        qkv = self.wqkv(x)
+        qkv = self.wqkv(x) if fused is None else self.wqkv.forward_quantized(fused[0], fused[1])
         q = qkv[..., : H * D].view(B, T, H, D)
         k = qkv[..., H * D: (H + Hkv) * D].view(B, T, Hkv, D)
         v = qkv[..., (H + Hkv) * D:].view(B, T, Hkv, D)
@@ -115,6 +117,9 @@ class Attention(nn.Module):
         cv.index_copy_(2, pos, v.transpose(1, 2))
         o = F.scaled_dot_product_attention(q.transpose(1, 2), ck, cv, attn_mask=mask, enable_gqa=True)
         o = o.transpose(1, 2).reshape(B, T, H * D)
+        if fused is not None:
+            oq, os_ = rmsnorm_quant(o, self.attn_sub_norm.weight, fused[3])
+            return self.wo.forward_quantized(oq, os_, residual=fused[2])
         if self.attn_sub_norm is not None:
             o = self.attn_sub_norm(o)
         return self.wo(o)
@@ -136,6 +141,11 @@ class FeedForward(nn.Module):
             with torch.no_grad():
                 self.ffn_sub_norm.weight.copy_(dic[prefix + ".ffn_sub_norm.weight"])
 
+    def forward_fused(self, xq, s, residual, eps):
+        x13 = self.w13.forward_quantized(xq, s)
+        iq, is_ = rmsnorm_quant(x13, self.ffn_sub_norm.weight, eps, gated=True)
+        return self.w2.forward_quantized(iq, is_, residual=residual)
+
     def forward(self, x):
         x1, x3 = self.w13(x).chunk(2, -1)
         inner = F.relu(x1) ** 2 * x3
@@ -155,7 +165,13 @@ class TransformerBlock(nn.Module):
             self.attention_norm.weight.copy_(dic[prefix + ".attention_norm.weight"])
             self.ffn_norm.weight.copy_(dic[prefix + ".ffn_norm.weight"])
 
-    def forward(self, x, cache, pos, cos, sin, mask):
+    def forward(self, x, cache, pos, cos, sin, mask, fused: bool = False):
+        if fused:
+            eps = self.attention_norm.eps
+            xq, s = rmsnorm_quant(x, self.attention_norm.weight, eps)
+            h = self.attention(x, cache, pos, cos, sin, mask, fused=(xq, s, x, eps))
+            hq, hs = rmsnorm_quant(h, self.ffn_norm.weight, eps)
+            return self.feed_forward.forward_fused(hq, hs, h, eps)
         h = x + self.attention(self.attention_norm(x), cache, pos, cos, sin, mask)
         return h + self.feed_forward(self.ffn_norm(h))
 
@@ -199,6 +215,6 @@ class Transformer(nn.Module):
         mask = (keys[None, :] <= pos[:, None])[None, None]          # [1, 1, T, L] causal over cache positions
         h = self.tok_embeddings(tokens)
         for layer, c in zip(self.layers, cache):
-            h = layer(h, c, pos, cos, sin, mask)
+            h = layer(h, c, pos, cos, sin, mask, self.args.fused_glue and self.tp == 1)
         h = self.norm(h)
         return F.linear(h, self.tok_embeddings.weight).float()

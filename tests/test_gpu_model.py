@@ -74,3 +74,78 @@ def test_small_model_greedy_tokens_identical(lib):
         t1, _ = FastGen(ours, GenArgs(16, bsz, 64, True)).generate(prompt)
         t2, _ = FastGen(ref, GenArgs(16, bsz, 64, False)).generate(prompt)
         assert torch.equal(t1, t2)
+
+
+def torch_norm_quant(x, w, eps, gated=False):
+    """The unfused glue: (gate ->) RMSNorm in fp32 -> bf16 -> eager quantiser."""
+    from ternainfer_b200.linear import quant_input
+    if gated:
+        x1, x3 = x.chunk(2, -1)
+        x = torch.relu(x1) ** 2 * x3
+    xf = x.float()
+    y = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(x.dtype)
+    return quant_input(y)
+
+
+@pytest.mark.parametrize("gated", [False, True])
+@pytest.mark.parametrize("M,K", [(1, 2560), (8, 2560), (8, 6912), (33, 8192), (5, 28672), (3, 64)])
+def test_fused_norm_quant_against_torch(lib, gated, M, K):
+    """Floating-point kernel: the scale must agree within one bf16 ulp and the int8 values
+    within one step on at most 0.5 % of the elements (the sum of squares is accumulated in a
+    different order than torch's reduction); everything else must be identical."""
+    from ternainfer_b200.linear import rmsnorm_quant
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + K)
+    x = torch.randn((M, 2 * K if gated else K), generator=g, device="cuda").to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(K, generator=g, device="cuda")).to(torch.bfloat16)
+    q, s = rmsnorm_quant(x, w, 1e-5, gated=gated)
+    q_ref, s_ref = torch_norm_quant(x, w, 1e-5, gated)
+    assert q.shape == q_ref.shape and s.shape == s_ref.shape
+    rel = ((s.float() - s_ref.float()).abs() / s_ref.float()).max().item()
+    assert rel <= 2.0 ** -7
+    d = (q.int() - q_ref.int()).abs()
+    assert d.max().item() <= 1
+    assert (d != 0).float().mean().item() <= 0.005 or rel > 0   # a scale one ulp apart moves more values by one step
+    same_scale = (s == s_ref).reshape(-1)
+    if same_scale.any():
+        assert (d[same_scale] != 0).float().mean().item() <= 0.005
+
+
+def test_residual_epilogue_bit_exact(lib):
+    from ternainfer_b200.linear import SpBitLinear, quant_input
+    from ternainfer_b200.convert import compress_weight
+    import ternaspmm_oracle as o
+    N, K, M = 2560, 2560, 8
+    w = o.make_ternary(N, K, 0.45, seed=91)
+    cv, tg, tm, bm = compress_weight(torch.from_numpy(w))
+    dic = {"l.weight_compressed_val": cv, "l.weight_TileOffsets_global": tg, "l.weight_TileOffsets_median": tm,
+           "l.weight_bitmap": bm, "l.weight_scale": torch.tensor([0.03, 0, 0, 0]).to(torch.bfloat16)}
+    layer = SpBitLinear(K, N, dic, "l")
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn((M, K), generator=g, device="cuda").to(torch.bfloat16)
+    res = torch.randn((M, N), generator=g, device="cuda").to(torch.bfloat16)
+    xq, s = quant_input(x)
+    assert torch.equal(layer.forward_quantized(xq, s, residual=res), res + layer(x))
+    for big in (100, 300):    # the tensor-core kernel's epilogue
+        xb = torch.randn((big, K), generator=g, device="cuda").to(torch.bfloat16)
+        rb = torch.randn((big, N), generator=g, device="cuda").to(torch.bfloat16)
+        xq, s = quant_input(xb)
+        assert torch.equal(layer.forward_quantized(xq, s, residual=rb), rb + layer(xb))
+
+
+@torch.inference_mode()
+def test_fused_glue_model_close_to_unfused(lib):
+    """The fused-glue model computes the same function up to the summation order of the norms:
+    logits must agree closely and the greedy continuation must start identically."""
+    import copy
+    args, ours, _ = build(2, 1024, max_len=96)
+    fused = copy.copy(ours)
+    fused.args = copy.copy(args)
+    fused.args.fused_glue = True
+    g = torch.Generator(device="cuda").manual_seed(13)
+    tok = torch.randint(0, 1024, (2, 48), generator=g, device="cuda")
+    pos = torch.arange(48, device="cuda")
+    a = ours(tok, ours.make_cache(2, "cuda"), pos)
+    b = fused(tok, fused.make_cache(2, "cuda"), pos)
+    err = (a - b).abs().max().item() / a.abs().max().item()
+    assert err < 0.05, err
+    assert (a.argmax(-1) == b.argmax(-1)).float().mean().item() > 0.9
