@@ -494,6 +494,44 @@ def run_tp_arm(args):
     _finish(world)
 
 
+# ----------------------------------------------------------------------------
+# End-to-end decode arm (BASELINE config 4): the 30-layer BitNet-2B architecture
+# with random-init ternary weights and a dense bf16 tied embedding / head, prompt
+# of seeded random ids, greedy generation; value = decode tokens per second.
+# ----------------------------------------------------------------------------
+
+def run_decode_arm(args):
+    import torch
+    from ternainfer_b200.generate import FastGen, GenArgs, build_random_model
+    from ternainfer_b200.model import ModelArgs
+    torch.cuda.set_device(0)
+    bsz = args.tokens if args.tokens in (1, 8) else 1
+    margs = ModelArgs(n_layers=args.layers, fused_glue=not args.unfused)
+    model, _ = build_random_model(margs, 512 + 128, args.seed)
+    gen = FastGen(model, GenArgs(128, bsz, 512, True))
+    g = torch.Generator(device="cuda").manual_seed(args.seed + 1)
+    prompt = torch.randint(0, margs.vocab_size, (bsz, 512), generator=g, device="cuda")
+    for _ in range(max(1, args.warmup // 3)):
+        gen.generate(prompt)
+    sampler = ClockSampler(0)
+    sampler.start()
+    best = None
+    for _ in range(max(1, args.steps // 10)):
+        _, st = gen.generate(prompt)
+        if best is None or st["decode_tokens_per_s"] > best["decode_tokens_per_s"]:
+            best = st
+    clocks = sampler.stop()
+    line = {"metric": "decode_tokens_per_s", "value": best["decode_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * bsz / best["decode_tokens_per_s"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8xternary->int32->bf16",
+            "data": "synthetic",
+            "config": {"workload": f"bitnet2b_greedy_decode_bs{bsz}", "layers": args.layers, "prompt": 512,
+                       "generate": 128, "fused_glue": not args.unfused, "seed": args.seed,
+                       "prefill_tokens_per_s": best["prefill_tokens_per_s"]},
+            "clocks": clocks}
+    print(json.dumps(line), flush=True)
+
+
 def _finish(world):
     """Leave without tearing NCCL down: destroying a process group while CUDA
     graphs that hold NCCL kernels are alive blocks at exit, so every rank meets
@@ -518,7 +556,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=8)
     ap.add_argument("--layers", type=int, default=30)
     ap.add_argument("--seed", type=int, default=1234)
-    ap.add_argument("--workload", default="sweep", choices=["sweep", "tp"])
+    ap.add_argument("--workload", default="sweep", choices=["sweep", "tp", "decode"])
+    ap.add_argument("--unfused", action="store_true", help="decode workload: plain torch glue between the linears")
     ap.add_argument("--tp_mode", default="single", choices=["single", "exact"])
     ap.add_argument("--no_graph", action="store_true", help="tp workload: launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--verbose", action="store_true")
@@ -528,6 +567,8 @@ def main():
         run_reference_arm(args)
     elif args.workload == "tp":
         run_tp_arm(args)
+    elif args.workload == "decode":
+        run_decode_arm(args)
     else:
         run_gpu_arm(args)
 

@@ -117,6 +117,24 @@ class Attention(nn.Module):
         cv.index_copy_(2, pos, v.transpose(1, 2))
         o = F.scaled_dot_product_attention(q.transpose(1, 2), ck, cv, attn_mask=mask, enable_gqa=True)
         o = o.transpose(1, 2).reshape(B, T, H * D)
+        return self._project(o, fused)
+
+    def forward_flash(self, x, cache: LayerCache, seqlens, cos_tab, sin_tab, fused):
+        """Attention glue through flash_attn's kv-cache kernel (library code, not part of the
+        TernaSpMM path): RoPE on adjacent pairs, cache append and causal attention in one
+        launch.  Cache layout [B, L, Hkv, D]."""
+        from flash_attn import flash_attn_with_kvcache
+        B, T = x.shape[0], x.shape[1]
+        H, Hkv, D = self.n_heads, self.n_kv_heads, self.head_dim
+        qkv = self.wqkv.forward_quantized(fused[0], fused[1])
+        q = qkv[..., : H * D].view(B, T, H, D)
+        k = qkv[..., H * D: (H + Hkv) * D].view(B, T, Hkv, D)
+        v = qkv[..., (H + Hkv) * D:].view(B, T, Hkv, D)
+        o = flash_attn_with_kvcache(q, cache[0], cache[1], k=k, v=v, rotary_cos=cos_tab, rotary_sin=sin_tab,
+                                    cache_seqlens=seqlens, causal=True, rotary_interleaved=True)
+        return self._project(o.reshape(B, T, H * D), fused)
+
+    def _project(self, o, fused):
         if fused is not None:
             oq, os_ = rmsnorm_quant(o, self.attn_sub_norm.weight, fused[3])
             return self.wo.forward_quantized(oq, os_, residual=fused[2])
@@ -165,11 +183,14 @@ class TransformerBlock(nn.Module):
             self.attention_norm.weight.copy_(dic[prefix + ".attention_norm.weight"])
             self.ffn_norm.weight.copy_(dic[prefix + ".ffn_norm.weight"])
 
-    def forward(self, x, cache, pos, cos, sin, mask, fused: bool = False):
+    def forward(self, x, cache, pos, cos, sin, mask, fused: bool = False, flash=None):
         if fused:
             eps = self.attention_norm.eps
             xq, s = rmsnorm_quant(x, self.attention_norm.weight, eps)
-            h = self.attention(x, cache, pos, cos, sin, mask, fused=(xq, s, x, eps))
+            if flash is not None:
+                h = self.attention.forward_flash(x, cache, flash[0], flash[1], flash[2], (xq, s, x, eps))
+            else:
+                h = self.attention(x, cache, pos, cos, sin, mask, fused=(xq, s, x, eps))
             hq, hs = rmsnorm_quant(h, self.ffn_norm.weight, eps)
             return self.feed_forward.forward_fused(hq, hs, h, eps)
         h = x + self.attention(self.attention_norm(x), cache, pos, cos, sin, mask)
@@ -197,10 +218,19 @@ class Transformer(nn.Module):
         self.max_seq_len = max_seq_len
         self.tp = tp
         self._rope = None
+        self.flash = False
+        if args.fused_glue and tp == 1:
+            try:
+                import flash_attn  # noqa: F401
+                self.flash = True
+            except Exception:
+                self.flash = False
 
     def make_cache(self, batch: int, device, dtype=torch.bfloat16) -> List[LayerCache]:
         a = self.args
         shape = (batch, a.n_kv_heads // self.tp, self.max_seq_len, a.head_dim)
+        if self.flash and self.args.fused_glue:
+            shape = (batch, self.max_seq_len, a.n_kv_heads, a.head_dim)
         return [(torch.zeros(shape, device=device, dtype=dtype), torch.zeros(shape, device=device, dtype=dtype))
                 for _ in range(a.n_layers)]
 
@@ -209,12 +239,17 @@ class Transformer(nn.Module):
         Returns fp32 logits [B, T, vocab] (model.py:380-386 of the reference)."""
         if self._rope is None or self._rope[0].device != tokens.device:
             self._rope = rope_tables(self.args.head_dim, self.max_seq_len, self.args.rope_theta, tokens.device)
+            self._rope_lp = (self._rope[0].to(torch.bfloat16), self._rope[1].to(torch.bfloat16))
         B, T = tokens.shape
         cos, sin = self._rope[0][pos].expand(B, T, -1), self._rope[1][pos].expand(B, T, -1)
         keys = torch.arange(self.max_seq_len, device=tokens.device)
         mask = (keys[None, :] <= pos[:, None])[None, None]          # [1, 1, T, L] causal over cache positions
         h = self.tok_embeddings(tokens)
+        fused = self.args.fused_glue and self.tp == 1
+        flash = None
+        if fused and self.flash:
+            flash = (pos[:1].to(torch.int32).expand(B).contiguous(), self._rope_lp[0], self._rope_lp[1])
         for layer, c in zip(self.layers, cache):
-            h = layer(h, c, pos, cos, sin, mask, self.args.fused_glue and self.tp == 1)
+            h = layer(h, c, pos, cos, sin, mask, fused, flash)
         h = self.norm(h)
         return F.linear(h, self.tok_embeddings.weight).float()

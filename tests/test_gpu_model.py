@@ -149,3 +149,29 @@ def test_fused_glue_model_close_to_unfused(lib):
     err = (a - b).abs().max().item() / a.abs().max().item()
     assert err < 0.05, err
     assert (a.argmax(-1) == b.argmax(-1)).float().mean().item() > 0.9
+
+
+@torch.inference_mode()
+def test_fused_glue_with_flash_attention_close_to_unfused(lib):
+    """Same check with the attention glue routed through flash_attn's kv-cache kernel
+    (RoPE + cache append + attention in one library launch), prefill then one decode step."""
+    pytest.importorskip("flash_attn")
+    from ternainfer_b200.model import ModelArgs, Transformer
+    from ternainfer_b200.convert.convert_TernaInfer import random_checkpoint
+    args = ModelArgs(n_layers=2, vocab_size=1024)
+    dic = random_checkpoint(args.dim, 2, args.n_heads, args.n_kv_heads, args.ffn_dim, 1024, seed=7)
+    fargs = ModelArgs(n_layers=2, vocab_size=1024, fused_glue=True)
+    with torch.device("cuda"):
+        plain = Transformer(args, dic, max_seq_len=96).to(torch.bfloat16)
+        fused = Transformer(fargs, dic, max_seq_len=96).to(torch.bfloat16)
+    assert fused.flash
+    g = torch.Generator(device="cuda").manual_seed(17)
+    tok = torch.randint(0, 1024, (2, 40), generator=g, device="cuda")
+    c1, c2 = plain.make_cache(2, "cuda"), fused.make_cache(2, "cuda")
+    pos = torch.arange(40, device="cuda")
+    a, b = plain(tok, c1, pos), fused(tok, c2, pos)
+    assert (a - b).abs().max().item() / a.abs().max().item() < 0.05
+    nxt = torch.randint(0, 1024, (2, 1), generator=g, device="cuda")
+    p1 = torch.tensor([40], device="cuda")
+    a, b = plain(nxt, c1, p1), fused(nxt, c2, p1)
+    assert (a - b).abs().max().item() / a.abs().max().item() < 0.05
