@@ -224,7 +224,7 @@ __device__ __forceinline__ uint32_t lut_entry_upper(uint32_t e) {
 // lower nibble of the next byte, table `lut_lo`) and the four bits below it at
 // bits 7-10 (they end the sign run of the upper nibble of the previous byte,
 // table `lut_hi`, whose entries take their signs from the top of that field).
-__device__ __forceinline__ void decode_word2(uint32_t bmw, uint32_t sgn, int total, uint32_t lut_lo, uint32_t lut_hi,
+__device__ __forceinline__ void decode_word2(uint32_t bmw, uint32_t sgn, int total, uint32_t lut_lo, uint32_t /*lut_hi*/,
                                              uint32_t (&a)[8]) {
     const uint32_t t1 = bmw - ((bmw >> 1) & 0x55555555u);
     const uint32_t y = (t1 & 0x33333333u) + ((t1 >> 2) & 0x33333333u);  // popcount of each nibble
@@ -239,8 +239,10 @@ __device__ __forceinline__ void decode_word2(uint32_t bmw, uint32_t sgn, int tot
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
         const uint32_t bs = b == 0 ? (bmw << 7) : (bmw >> (8 * b - 7));  // nibble 2b at bits 7-10, nibble 2b+1 at 11-14
-        a[2 * b] = lds32((bs & 0x780u) | ((yb[b] & 0x7800u) | lut_lo));
-        a[2 * b + 1] = lds32((bs & 0x7800u) | ((yb[b + 1] & 0x780u) | lut_hi));
+        const uint32_t base = (bs & 0x7F80u) | lut_lo;                    // both nibbles + table base + lane, once per byte
+        // one bit-select per lookup: the sign field replaces the other nibble's field
+        a[2 * b] = lds32((yb[b] & 0x7800u) | (base & ~0x7800u));
+        a[2 * b + 1] = lds32_plus<kLutBytes>((yb[b + 1] & 0x780u) | (base & ~0x780u));   // second table, 32 KB further
     }
 }
 
