@@ -423,7 +423,8 @@ def run_tp_arm(args):
         layers.append((tp.ColumnParallelSpBitLinear(dim, specs[0][2], dic, "wqkv"),
                        tp.RowParallelSpBitLinear(dim // world, dim, dic, "wo", None, ones_d, 1e-5, args.tp_mode),
                        tp.ColumnParallelSpBitLinear(dim, specs[2][2], dic, "w13"),
-                       tp.RowParallelSpBitLinear(ffn // world, dim, dic, "w2", None, ones_f, 1e-5, args.tp_mode)))
+                       tp.RowParallelSpBitLinear(ffn // world, dim, dic, "w2", None, ones_f, 1e-5, args.tp_mode,
+                                                 gated=True)))
     gen.manual_seed(args.seed)
     x0 = torch.randn((M, dim), generator=gen, device=device).to(torch.bfloat16)
     attn = torch.randn((M, dim // world), generator=gen, device=device).to(torch.bfloat16)
@@ -434,9 +435,8 @@ def run_tp_arm(args):
         x = x0
         for qkv, wo, w13, w2 in layers:
             qkv(x)
-            h = x + wo(attn)
-            x1, x3 = w13(h).chunk(2, -1)
-            x = h + w2(torch.relu(x1) ** 2 * x3)
+            h = wo(attn, residual=x)
+            x = w2(w13(h), residual=h)
         return x
 
     def log(msg):
@@ -499,7 +499,7 @@ def run_tp_arm(args):
                 "roofline": {"bound": "hbm", "achieved": val / world, "peak": peak, "unit": "GB/s",
                              "frac": val / world / peak, "peak_kind": "of " + kind, "traffic": None,
                              "note": "per-GPU compressed-weight bytes per second"},
-                "gpu_launches": 4 * L * args.steps, "clocks": clocks}
+                "gpu_launches": (10 if args.tp_mode == "single" else 6) * L * args.steps, "clocks": clocks}
         print(json.dumps(line), flush=True)
     _finish(world)
 

@@ -153,6 +153,28 @@ void ternaspmm_rmsnorm_quant(ternaspmm_bf16* x, ternaspmm_bf16* norm_weight, flo
 void ternaspmm_relu2_gate_rmsnorm_quant(ternaspmm_bf16* x13, ternaspmm_bf16* norm_weight, float eps, int M,
                                         int K, int8_t* q, ternaspmm_bf16* s_out, ternaspmm_stream_t stream);
 
+/* Plain per-token absmax quantiser (model.py:120-123) as one kernel. */
+void ternaspmm_quant(ternaspmm_bf16* x, int M, int K, int8_t* q, ternaspmm_bf16* s_out,
+                     ternaspmm_stream_t stream);
+
+/* Front-end of a row-parallel (K-sharded) linear: y = x * weight WITHOUT the RMS factor
+ * (gated != 0: x holds [x1 | x3] and the value is relu(x1)^2 * x3), quantised per token with
+ * the shard's own absmax; ss_out[t] = this shard's sum of squares, to be all-reduced. */
+void ternaspmm_scale_quant_sumsq(ternaspmm_bf16* x, ternaspmm_bf16* weight, int gated, int M, int K,
+                                 int8_t* q, ternaspmm_bf16* s_out, float* ss_out,
+                                 ternaspmm_stream_t stream);
+
+/* Contraction with fp32 output out[t][n] = float(acc) / s[t] (no weight scale): the partial
+ * result of one K shard, ready for a sum all-reduce. */
+void ternaspmm_partial_f32(int8_t* x, uint64_t* bitmap, int* tile_offsets, uint16_t* quarter_offsets,
+                           uint32_t* sign_words, float* out, ternaspmm_bf16* s, int M, int N, int K,
+                           ternaspmm_stream_t stream);
+
+/* Tail of a row-parallel linear after the all-reduce: buf = fp32 [M*N] summed partials followed
+ * by fp32 [M] summed squares; out = bf16(buf * rsqrt(ss/full_width + eps) * ws[0]) (+ residual). */
+void ternaspmm_tp_finish(float* buf, ternaspmm_bf16* ws, float eps, int full_width, int M, int N,
+                         ternaspmm_bf16* residual, ternaspmm_bf16* out, ternaspmm_stream_t stream);
+
 /* Host packer from int8 ternary [N][K] into caller-provided arrays
  * (bitmap N*K/64, tile_offsets tiles+1, quarter_offsets 3*tiles, sign_words
  * at least N*K/32 + 4 words, zero-filled by the call).  Returns the number of

@@ -38,13 +38,19 @@ __device__ __forceinline__ float block_reduce(float v, float* scratch, bool is_m
     return r;
 }
 
+// MODE 0: y = RMSNorm(v) * w.  MODE 1: y = v * w without the normalisation, and the row's sum
+// of squares of v is written to ss_out (tensor-parallel row shards: the RMS factor needs the sum
+// over all shards and is applied after the all-reduce).  MODE 2: y = v (plain quantiser).
+enum ActMode : int { ACT_RMSNORM = 0, ACT_SCALE_SUMSQ = 1, ACT_PLAIN = 2 };
+
 // x: [M][ld] bf16 (GATED: the row holds [x1 (K) | x3 (K)], ld = 2K), w: [K] bf16 norm weight,
-// q: [M][K] int8, s_out: [M] bf16.  Dynamic shared memory: K bf16.
-template <bool GATED>
+// q: [M][K] int8, s_out: [M] bf16, ss_out: [M] fp32 (MODE 1).  Dynamic shared memory: K bf16.
+template <bool GATED, int MODE>
 __global__ void __launch_bounds__(kActThreads) norm_quant_kernel(const __nv_bfloat16* __restrict__ x,
                                                                   const __nv_bfloat16* __restrict__ w, float eps,
                                                                   int K, int8_t* __restrict__ q,
-                                                                  __nv_bfloat16* __restrict__ s_out) {
+                                                                  __nv_bfloat16* __restrict__ s_out,
+                                                                  float* __restrict__ ss_out) {
     extern __shared__ __align__(16) uint8_t act_smem[];
     __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(act_smem);
     __shared__ float scratch[kActThreads / 32];
@@ -79,23 +85,31 @@ __global__ void __launch_bounds__(kActThreads) norm_quant_kernel(const __nv_bflo
         }
         *reinterpret_cast<uint4*>(row + k0) = *reinterpret_cast<const uint4*>(v);
     }
-    ss = block_reduce(ss, scratch, false);
-    const float rstd = rsqrtf(ss / (float)K + eps);
+    float rstd = 1.f;
+    if (MODE != ACT_PLAIN) {
+        ss = block_reduce(ss, scratch, false);
+        if (MODE == ACT_RMSNORM) rstd = rsqrtf(ss / (float)K + eps);
+        if (MODE == ACT_SCALE_SUMSQ && tid == 0) ss_out[t] = ss;
+    }
 
     // pass 2: normalise, apply the weight, round to bf16, absmax
     float amax = 0.f;
     for (int k0 = tid * 8; k0 < K; k0 += kActThreads * 8) {
         uint4 a = *reinterpret_cast<const uint4*>(row + k0);
-        const uint4 wv = *reinterpret_cast<const uint4*>(w + k0);
         __nv_bfloat16* av = reinterpret_cast<__nv_bfloat16*>(&a);
-        const __nv_bfloat16* ww = reinterpret_cast<const __nv_bfloat16*>(&wv);
+        if (MODE != ACT_PLAIN) {
+            const uint4 wv = *reinterpret_cast<const uint4*>(w + k0);
+            const __nv_bfloat16* ww = reinterpret_cast<const __nv_bfloat16*>(&wv);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float y = (__bfloat162float(av[i]) * rstd) * __bfloat162float(ww[i]);
-            av[i] = __float2bfloat16_rn(y);
-            amax = fmaxf(amax, fabsf(__bfloat162float(av[i])));
+            for (int i = 0; i < 8; ++i) {
+                const float y = (MODE == ACT_RMSNORM ? __bfloat162float(av[i]) * rstd : __bfloat162float(av[i])) *
+                                __bfloat162float(ww[i]);
+                av[i] = __float2bfloat16_rn(y);
+            }
+            *reinterpret_cast<uint4*>(row + k0) = a;
         }
-        *reinterpret_cast<uint4*>(row + k0) = a;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(__bfloat162float(av[i])));
     }
     amax = block_reduce(amax, scratch, true);
     amax = bf16_round_f(fmaxf(amax, 1e-5f));
@@ -111,6 +125,25 @@ __global__ void __launch_bounds__(kActThreads) norm_quant_kernel(const __nv_bflo
             o[i] = (int8_t)fminf(fmaxf(rintf(p), -128.f), 127.f);
         }
         *reinterpret_cast<uint4*>(q + (size_t)t * K + k0) = *reinterpret_cast<const uint4*>(o);
+    }
+}
+
+// Tail of a row-parallel linear after the all-reduce: buf holds the summed fp32 partial outputs
+// [M][N] followed by the summed per-token sums of squares [M];
+// out = bf16(buf[t][n] * rsqrt(ss[t] / full_width + eps) * ws) (+ residual, rounded again).
+__global__ void __launch_bounds__(256) tp_finish_kernel(const float* __restrict__ buf, const __nv_bfloat16* ws,
+                                                        float eps, int full_width, int M, int N,
+                                                        const __nv_bfloat16* residual, __nv_bfloat16* out) {
+    griddep_launch_dependents();
+    griddep_wait();
+    const float w = __bfloat162float(ws[0]);
+    const long long total = (long long)M * N;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / N);
+        const float rstd = rsqrtf(buf[total + t] / (float)full_width + eps);
+        __nv_bfloat16 v = __float2bfloat16_rn((buf[i] * rstd) * w);
+        if (residual) v = __float2bfloat16_rn(__bfloat162float(residual[i]) + __bfloat162float(v));
+        out[i] = v;
     }
 }
 

@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(kLgThreads, 1)
         const int n = rb * 128 + 32 * quarter + lane;
         const bool n_ok = n < N;
         float ws_el = 0.f;
-        if (p.epilogue != EPI_RAW_I32 && n_ok)
+        if (p.epilogue != EPI_RAW_I32 && p.epilogue != EPI_F32_DIV && n_ok)
             ws_el = __bfloat162float(p.ws[ws_group(n, p)]);
         if (ok) {
 #pragma unroll 1
@@ -302,6 +302,7 @@ __global__ void __launch_bounds__(kLgThreads, 1)
                     if (n_ok && t < M) {
                         const long long o = (long long)t * N + n;
                         if (p.epilogue == EPI_RAW_I32) reinterpret_cast<int*>(p.out)[o] = v[j];
+                        else if (p.epilogue == EPI_F32_DIV) reinterpret_cast<float*>(p.out)[o] = __fdiv_rn(__int2float_rn(v[j]), s_s[c0 + j]);
                         else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = add_residual(scale_epilogue(v[j], s_s[c0 + j], ws_el, p.epilogue), p.residual, o);
                     }
                 }

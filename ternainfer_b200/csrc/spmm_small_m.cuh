@@ -25,7 +25,7 @@
 
 namespace tsp {
 
-enum Epilogue : int { EPI_DECODE = 0, EPI_PREFILL = 1, EPI_RAW_I32 = 2 };
+enum Epilogue : int { EPI_DECODE = 0, EPI_PREFILL = 1, EPI_RAW_I32 = 2, EPI_F32_DIV = 3 };   // 3: fp32 acc / s[t]
 enum Status : int { ST_OK = 0, ST_BAD_SHAPE = 1, ST_BAD_POINTER = 2, ST_LAUNCH = 3, ST_WAIT_TIMEOUT = 4 };
 
 struct SpmmParams {
@@ -338,7 +338,7 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const Spm
     griddep_wait();
     phase_mark(4);
     if (tid < mrows && p.epilogue != EPI_RAW_I32) scl_s[tid] = __bfloat162float(p.s[m0 + tid]);
-    if (tid >= 32 && tid < 36 && p.epilogue != EPI_RAW_I32) scl_s[MT * 8 + tid - 32] = __bfloat162float(p.ws[tid - 32]);
+    if (tid >= 32 && tid < 36 && p.epilogue != EPI_RAW_I32 && p.epilogue != EPI_F32_DIV) scl_s[MT * 8 + tid - 32] = __bfloat162float(p.ws[tid - 32]);
 
     if (have_first) {
         uint4 bx[MT];
@@ -408,6 +408,8 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const Spm
         const long long o = (long long)(m0 + t) * N + n;
         if (p.epilogue == EPI_RAW_I32) {
             reinterpret_cast<int*>(p.out)[o] = v;
+        } else if (p.epilogue == EPI_F32_DIV) {
+            reinterpret_cast<float*>(p.out)[o] = __fdiv_rn(__int2float_rn(v), scl_s[t]);
         } else {
             const float s_el = scl_s[t];
             const float ws_el = scl_s[MT * 8 + ws_group(n, p)];

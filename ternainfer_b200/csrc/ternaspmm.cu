@@ -194,13 +194,13 @@ static void run_spmm(int8_t* x, uint64_t* bitmap, int* tile_off, uint16_t* quart
                      cudaStream_t stream, const int* seg_bounds = nullptr, const __nv_bfloat16* residual = nullptr) {
     t_host_status = ST_OK;
     if (M < 1 || N < 64 || K < 64 || (N % 64) || (K % 64) ||
-        (epilogue != EPI_RAW_I32 && (ws_num < 1 || ws_num > 4))) {
+        (epilogue != EPI_RAW_I32 && epilogue != EPI_F32_DIV && (ws_num < 1 || ws_num > 4))) {
         fprintf(stderr, "ternaspmm: unsupported shape M=%d N=%d K=%d ws_num=%d (need M>=1, N%%64==0, K%%64==0, 1<=ws_num<=4)\n",
                 M, N, K, ws_num);
         t_host_status = ST_BAD_SHAPE;
         return;
     }
-    if (!x || !bitmap || !tile_off || !quarter_off || !signs || !out || (epilogue != EPI_RAW_I32 && (!s || !ws)) ||
+    if (!x || !bitmap || !tile_off || !quarter_off || !signs || !out || ((epilogue == EPI_DECODE || epilogue == EPI_PREFILL) && (!s || !ws)) || (epilogue == EPI_F32_DIV && !s) ||
         (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(bitmap) & 15) ||
         (reinterpret_cast<uintptr_t>(signs) & 15)) {
         fprintf(stderr, "ternaspmm: null or misaligned pointer (x, bitmap and sign_words must be 16-byte aligned)\n");
@@ -341,28 +341,34 @@ extern "C" void ternaspmm_linear_segments(int8_t* x, uint64_t* bitmap, int* tile
     checkLastCudaError(__LINE__);
 }
 
-static void run_norm_quant(bool gated, __nv_bfloat16* x, __nv_bfloat16* w, float eps, int M, int K, int8_t* q,
-                           __nv_bfloat16* s_out, cudaStream_t stream) {
+static void run_norm_quant(bool gated, int mode, __nv_bfloat16* x, __nv_bfloat16* w, float eps, int M, int K,
+                           int8_t* q, __nv_bfloat16* s_out, float* ss_out, cudaStream_t stream) {
     t_host_status = ST_OK;
     if (M < 1 || K < 16 || (K % 16) || K > 56 * 1024) {
         fprintf(stderr, "ternaspmm: norm_quant needs M>=1 and K a multiple of 16 up to 57344 (got M=%d K=%d)\n", M, K);
         t_host_status = ST_BAD_SHAPE;
         return;
     }
-    if (!x || !w || !q || !s_out || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
+    if (!x || (mode != ACT_PLAIN && !w) || !q || !s_out || (mode == ACT_SCALE_SUMSQ && !ss_out) ||
+        (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
         (reinterpret_cast<uintptr_t>(q) & 15)) {
         fprintf(stderr, "ternaspmm: norm_quant: null or misaligned pointer\n");
         t_host_status = ST_BAD_POINTER;
         return;
     }
-    static bool attr_done[64][2] = {};
+    typedef void (*Kern)(const __nv_bfloat16*, const __nv_bfloat16*, float, int, int8_t*, __nv_bfloat16*, float*);
+    Kern kern = gated ? (mode == ACT_RMSNORM ? norm_quant_kernel<true, ACT_RMSNORM> : norm_quant_kernel<true, ACT_SCALE_SUMSQ>)
+                      : (mode == ACT_RMSNORM ? norm_quant_kernel<false, ACT_RMSNORM>
+                                             : (mode == ACT_SCALE_SUMSQ ? norm_quant_kernel<false, ACT_SCALE_SUMSQ>
+                                                                        : norm_quant_kernel<false, ACT_PLAIN>));
+    static bool attr_done[64][8] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
-    auto kern = gated ? norm_quant_kernel<true> : norm_quant_kernel<false>;
-    if (!attr_done[dev][gated]) {
+    const int slot = (gated ? 4 : 0) + mode;
+    if (!attr_done[dev][slot]) {
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 56 * 1024);
-        attr_done[dev][gated] = true;
+        attr_done[dev][slot] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(M, 1, 1);
@@ -374,19 +380,63 @@ static void run_norm_quant(bool gated, __nv_bfloat16* x, __nv_bfloat16* w, float
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = tuning().pdl ? 1 : 0;
-    if (cudaLaunchKernelEx(&cfg, kern, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, eps, K, q, s_out) != cudaSuccess)
+    if (cudaLaunchKernelEx(&cfg, kern, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, eps, K, q, s_out, ss_out) !=
+        cudaSuccess)
         t_host_status = ST_LAUNCH;
 }
 
 extern "C" void ternaspmm_rmsnorm_quant(__nv_bfloat16* x, __nv_bfloat16* norm_weight, float eps, int M, int K,
                                        int8_t* q, __nv_bfloat16* s_out, cudaStream_t stream) {
-    run_norm_quant(false, x, norm_weight, eps, M, K, q, s_out, stream);
+    run_norm_quant(false, ACT_RMSNORM, x, norm_weight, eps, M, K, q, s_out, nullptr, stream);
     checkLastCudaError(__LINE__);
 }
 
 extern "C" void ternaspmm_relu2_gate_rmsnorm_quant(__nv_bfloat16* x13, __nv_bfloat16* norm_weight, float eps, int M,
                                                   int K, int8_t* q, __nv_bfloat16* s_out, cudaStream_t stream) {
-    run_norm_quant(true, x13, norm_weight, eps, M, K, q, s_out, stream);
+    run_norm_quant(true, ACT_RMSNORM, x13, norm_weight, eps, M, K, q, s_out, nullptr, stream);
+    checkLastCudaError(__LINE__);
+}
+
+extern "C" void ternaspmm_quant(__nv_bfloat16* x, int M, int K, int8_t* q, __nv_bfloat16* s_out, cudaStream_t stream) {
+    run_norm_quant(false, ACT_PLAIN, x, nullptr, 0.f, M, K, q, s_out, nullptr, stream);
+    checkLastCudaError(__LINE__);
+}
+
+extern "C" void ternaspmm_scale_quant_sumsq(__nv_bfloat16* x, __nv_bfloat16* weight, int gated, int M, int K,
+                                           int8_t* q, __nv_bfloat16* s_out, float* ss_out, cudaStream_t stream) {
+    run_norm_quant(gated != 0, ACT_SCALE_SUMSQ, x, weight, 0.f, M, K, q, s_out, ss_out, stream);
+    checkLastCudaError(__LINE__);
+}
+
+extern "C" void ternaspmm_partial_f32(int8_t* x, uint64_t* bitmap, int* tile_offsets, uint16_t* quarter_offsets,
+                                     uint32_t* sign_words, float* out, __nv_bfloat16* s, int M, int N, int K,
+                                     cudaStream_t stream) {
+    run_spmm(x, bitmap, tile_offsets, quarter_offsets, sign_words, out, s, nullptr, 1, M, N, K, EPI_F32_DIV, stream);
+    checkLastCudaError(__LINE__);
+}
+
+extern "C" void ternaspmm_tp_finish(float* buf, __nv_bfloat16* ws, float eps, int full_width, int M, int N,
+                                   __nv_bfloat16* residual, __nv_bfloat16* out, cudaStream_t stream) {
+    t_host_status = ST_OK;
+    if (!buf || !ws || !out || M < 1 || N < 1) {
+        t_host_status = ST_BAD_POINTER;
+        return;
+    }
+    const long long total = (long long)M * N;
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > 4 * device_sm_count()) blocks = 4 * device_sm_count();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks, 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tuning().pdl ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, tp_finish_kernel, (const float*)buf, (const __nv_bfloat16*)ws, eps, full_width, M, N,
+                           (const __nv_bfloat16*)residual, out) != cudaSuccess)
+        t_host_status = ST_LAUNCH;
     checkLastCudaError(__LINE__);
 }
 

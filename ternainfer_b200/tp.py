@@ -12,11 +12,14 @@ cross-rank statistics.  Two modes:
 
 ``single`` (default) - one collective per linear.  Each rank quantises its
     un-normalised slice ``x_r * g_r`` with its *local* absmax, multiplies on the
-    GPU (int32 accumulators), divides by its own scale and appends its partial
-    sum of squares as one extra column; a single fp32 all-reduce of [M, N+1]
-    carries everything and the RMS factor and weight scale are applied after.
-    Mathematically identical to the unsharded layer, numerically within bf16
-    rounding of it (each rank rounds with its own scale).
+    GPU, divides by its own scale and appends its partial sums of squares; a
+    single fp32 all-reduce of M*N + M values carries everything and the RMS
+    factor and weight scale are applied after.  On the GPU this is three
+    launches around the collective (``ternaspmm_scale_quant_sumsq`` ->
+    ``ternaspmm_partial_f32`` -> all-reduce -> ``ternaspmm_tp_finish``, the last
+    one also adding the residual stream).  Mathematically identical to the
+    unsharded layer, numerically within bf16 rounding of it (each rank rounds
+    with its own scale).
 ``exact`` - bit-identical to the unsharded layer: all-reduce the sum of
     squares, normalise, all-reduce (max) the absmax, quantise with the global
     scale, all-reduce the int32 accumulators, then apply the decode epilogue.
@@ -92,6 +95,20 @@ def _linear_segments(xq, s, packed, ws, bounds, N: int) -> torch.Tensor:
     return out
 
 
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _quant_fused(x2: torch.Tensor):
+    """Per-token absmax int8 quantiser as one kernel (``ternaspmm_quant``)."""
+    lib = load_library()
+    M, K = x2.shape
+    xq = torch.empty((M, K), dtype=torch.int8, device=x2.device)
+    s = torch.empty((M, 1), dtype=torch.bfloat16, device=x2.device)
+    lib.ternaspmm_quant(x2.data_ptr(), M, K, xq.data_ptr(), s.data_ptr(), _stream())
+    return xq, s
+
+
 def _quant(x: torch.Tensor, amax: torch.Tensor = None):
     if amax is None:
         amax = x.abs().max(dim=-1, keepdim=True).values
@@ -118,32 +135,69 @@ class ColumnParallelSpBitLinear(nn.Module):
 
     def forward(self, x):
         shape = list(x.shape[:-1]) + [self.out_features]
-        xq, s = _quant(x.reshape(-1, self.in_features))
-        y = _linear_segments(xq, s.to(torch.bfloat16).contiguous(), self.packed, self.weight_scale, self.bounds,
-                             self.out_features)
+        x2 = x.reshape(-1, self.in_features)
+        if x2.is_cuda and x2.dtype == torch.bfloat16:
+            xq, s = _quant_fused(x2.contiguous())
+        else:
+            xq, s = _quant(x2)
+            s = s.to(torch.bfloat16).contiguous()
+        y = _linear_segments(xq, s, self.packed, self.weight_scale, self.bounds, self.out_features)
         return y.reshape(shape)
 
 
 class RowParallelSpBitLinear(nn.Module):
     """Input-column shard of ``wo`` / ``w2`` with the preceding sub-layer norm
     folded in (see the module docstring).  ``norm_weight`` is this rank's slice
-    of the norm weight; ``in_features`` is the local width K/tp."""
+    of the norm weight; ``in_features`` is the local width K/tp.  With
+    ``gated=True`` the input is this rank's ``[gate | up]`` block of width
+    2*K/tp and relu(gate)^2 * up is formed in the same kernel (``single`` mode
+    on the GPU only)."""
 
     def __init__(self, in_features: int, out_features: int, dic: dict, key: str, group=None,
-                 norm_weight: torch.Tensor = None, eps: float = 1e-5, mode: str = "single"):
+                 norm_weight: torch.Tensor = None, eps: float = 1e-5, mode: str = "single", gated: bool = False):
         super().__init__()
         self.in_features, self.out_features = in_features, out_features
         dev = "cuda" if torch.cuda.is_available() else "cpu"
         self.packed = [dic[key + s].to(dev) for s in (".weight_compressed_val", ".weight_TileOffsets_global",
                                                       ".weight_TileOffsets_median", ".weight_bitmap")]
-        self.ws = dic[key + ".weight_scale"].to(dev).float()[0]
-        self.norm_weight = norm_weight.to(dev).float()
-        self.group, self.eps, self.mode = group, eps, mode
+        self.ws_bf16 = dic[key + ".weight_scale"].to(dev).to(torch.bfloat16).contiguous()
+        self.ws = self.ws_bf16.float()[0]
+        self.norm_weight_bf16 = norm_weight.to(dev).to(torch.bfloat16).contiguous()
+        self.norm_weight = self.norm_weight_bf16.float()
+        self.group, self.eps, self.mode, self.gated = group, eps, mode, gated
         self.tp = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.fused = True       # False: the torch formulation of the same arithmetic (tests compare the two)
 
-    def forward(self, x):
+    def _forward_fused(self, x2: torch.Tensor, residual):
+        """GPU path of the ``single`` mode: three launches around one all-reduce."""
+        lib = load_library()
+        M, K, N = x2.shape[0], self.in_features, self.out_features
+        dev = x2.device
+        xq = torch.empty((M, K), dtype=torch.int8, device=dev)
+        s = torch.empty((M,), dtype=torch.bfloat16, device=dev)
+        buf = torch.empty((M * N + M,), dtype=torch.float32, device=dev)
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        cv, tg, tm, bm = self.packed
+        st = _stream()
+        lib.ternaspmm_scale_quant_sumsq(x2.data_ptr(), self.norm_weight_bf16.data_ptr(), int(self.gated), M, K,
+                                        xq.data_ptr(), s.data_ptr(), buf.data_ptr() + 4 * M * N, st)
+        lib.ternaspmm_partial_f32(xq.data_ptr(), bm.data_ptr(), tg.data_ptr(), tm.data_ptr(), cv.data_ptr(),
+                                  buf.data_ptr(), s.data_ptr(), M, N, K, st)
+        if self.tp > 1:
+            dist.all_reduce(buf, group=self.group)                 # the one collective of this linear
+        lib.ternaspmm_tp_finish(buf.data_ptr(), self.ws_bf16.data_ptr(), self.eps, K * self.tp, M, N,
+                                residual.data_ptr() if residual is not None else None, out.data_ptr(), st)
+        return out
+
+    def forward(self, x, residual=None):
         shape = list(x.shape[:-1]) + [self.out_features]
-        x2 = x.reshape(-1, self.in_features)
+        x2 = x.reshape(-1, self.in_features * (2 if self.gated else 1))
+        if self.fused and self.mode == "single" and x2.is_cuda and x2.dtype == torch.bfloat16:
+            res2 = residual.reshape(-1, self.out_features).contiguous() if residual is not None else None
+            return self._forward_fused(x2.contiguous(), res2).reshape(shape)
+        if self.gated:
+            x1, x3 = x2.chunk(2, dim=-1)
+            x2 = torch.relu(x1) ** 2 * x3
         full_width = self.in_features * self.tp
         xf = x2.float()
         ss = xf.pow(2).sum(-1, keepdim=True)
@@ -163,11 +217,14 @@ class RowParallelSpBitLinear(nn.Module):
             z = (xf * self.norm_weight).to(x.dtype)               # un-normalised: the RMS factor is applied last
             xq, s = _quant(z)
             acc = _accumulate_i32(xq, self.packed, self.out_features)
-            buf = torch.cat([acc.float() / s.float(), ss], dim=1)  # [M, N+1]: partial outputs + partial sum of squares
+            M, N = acc.shape
+            buf = torch.cat([(acc.float() / s.float()).reshape(-1), ss.reshape(-1)])  # partial outputs, then sums of squares
             if self.tp > 1:
                 dist.all_reduce(buf, group=self.group)             # the one collective of this linear
-            rstd = torch.rsqrt(buf[:, -1:] / full_width + self.eps)
-            out = (buf[:, :-1] * rstd * self.ws).to(torch.bfloat16)
+            rstd = torch.rsqrt(buf[M * N:].reshape(M, 1) / full_width + self.eps)
+            out = (buf[:M * N].reshape(M, N) * rstd * self.ws).to(torch.bfloat16)
+        if residual is not None:
+            out = residual.reshape(-1, self.out_features) + out
         return out.reshape(shape)
 
 
