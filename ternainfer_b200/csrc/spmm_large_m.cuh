@@ -9,20 +9,24 @@
 // (kernels/src/GEMM/gemm_scale_ws.h, epilogue_visitor_scale_ws.h:175-211).
 // No dense copy of the weights ever reaches HBM.
 //
-// CTA tile: 128 weight rows (the MMA's M) x NT tokens (the MMA's N) x all of
-// K, 128 k per pipeline stage.  Warp roles:
+// Persistent CTAs (one per SM) walk over output tiles of 128 weight rows (the
+// MMA's M) x NT tokens (the MMA's N); a tile runs over all of K in pipeline
+// steps of 128 k.  Tensor memory holds TWO accumulator buffers of NT columns,
+// so the epilogue of tile i overlaps the K loop of tile i+1.  Warp roles:
 //   warps 0-15 decoders: two warps share the 64x64 weight tile (row half,
 //              k half) of every second k-step, each taking two of the four
-//              16-row groups; they read bitmaps,
-//              offsets and sign words from global memory, decodes with the
-//              same table lookup as the small-batch kernel and stores int8
-//              rows of 128 k in the 128-byte-swizzled K-major layout.  After
-//              the K loop the same warps are the epilogue (tcgen05.ld ->
-//              scale -> bf16 store).
+//              16-row groups; they read bitmaps, offsets and sign words from
+//              global memory through a register pipeline that runs ahead
+//              across tile boundaries, decode with the same table lookup as
+//              the small-batch kernel and store int8 rows of 128 k in the
+//              128-byte-swizzled K-major layout.
 //   warp 16    activation loader: one thread issues 2-D TMA tile loads of
 //              x[NT tokens][128 k] (128-byte swizzle, no multicast).
 //   warp 17    one thread issues tcgen05.mma (four K=32 steps per stage) and
-//              commits stage releases / the final accumulator barrier.
+//              commits stage releases / the accumulator-full barrier.
+//   warps 18-25 epilogue: tcgen05.ld of one 32-lane quarter and one half of
+//              the token columns each -> scale -> bf16 (or int32 / fp32)
+//              stores, then hand the buffer back.
 // All hand-offs are mbarriers; every wait has an iteration limit and a CTA-wide
 // abort flag so that a lost signal ends the kernel with a status word.
 #pragma once
@@ -33,18 +37,19 @@
 namespace tsp {
 
 constexpr int kLgDecoders = 16;          // two warps per 64x64 tile, two k-steps in flight
-constexpr int kLgThreads = (kLgDecoders + 2) * 32;
+constexpr int kLgEpiWarps = 8;           // two per 32-lane quarter of tensor memory, half of the token columns each
+constexpr int kLgThreads = (kLgDecoders + 2 + kLgEpiWarps) * 32;
 constexpr int kLgKStep = 128;            // k per pipeline stage = one 128-byte swizzle row
 constexpr int kLgAStage = 128 * 128;     // bytes: 128 rows x 128 k int8
 
 template <int NT>
 struct LargeMSmem {
     static constexpr int stages = NT > 128 ? 3 : 4;
-    static constexpr int bars = 0;                         // full_a[4] full_b[4] empty[4] acc : 13 x 8 bytes
-    static constexpr int tmem_slot = 112;
-    static constexpr int abort_flag = 116;
-    static constexpr int scl = 128;                        // float s[NT]
-    static constexpr int lut1 = scl + NT * 4;              // the 256 table entries, one copy
+    static constexpr int bars = 0;                         // full_a[4] full_b[4] empty[4] acc_full[2] acc_empty[2]
+    static constexpr int tmem_slot = 136;
+    static constexpr int abort_flag = 140;
+    static constexpr int scl = 256;                        // float s[NT / 2] per epilogue warp
+    static constexpr int lut1 = scl + kLgEpiWarps * (NT / 2) * 4;   // the 256 table entries, one copy
     static constexpr int a = (lut1 + 1024 + 1023) / 1024 * 1024;
     static constexpr int b = a + stages * kLgAStage;
     static constexpr int rest = b + stages * NT * kLgKStep;
@@ -127,13 +132,19 @@ __global__ void __launch_bounds__(kLgThreads, 1)
     auto bar_full_a = [&](int s) { return sbase + L::bars + 8 * s; };
     auto bar_full_b = [&](int s) { return sbase + L::bars + 32 + 8 * s; };
     auto bar_empty = [&](int s) { return sbase + L::bars + 64 + 8 * s; };
-    const uint32_t bar_acc = sbase + L::bars + 96;
+    auto bar_acc_full = [&](int b) { return sbase + L::bars + 96 + 8 * b; };
+    auto bar_acc_empty = [&](int b) { return sbase + L::bars + 112 + 8 * b; };
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int rb = blockIdx.x, t0 = blockIdx.y * NT;
     const int N = p.N, K = p.K, M = p.M;
     const int KT = K >> 6;                 // 64-wide k-tiles of the packed format
     const int KS = (K + kLgKStep - 1) / kLgKStep;   // pipeline steps of 128 k
+    // Output tiles of this CTA: blockIdx.x, + gridDim.x, ...; row block fastest, so CTAs that run
+    // side by side share the activation tile in L2.
+    const int RB = (N + 127) / 128;
+    const int n_tiles = RB * ((M + NT - 1) / NT);
+    const int my_tiles = ((int)blockIdx.x < n_tiles) ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const int G = my_tiles * KS;           // pipeline steps of this CTA over all its tiles
 
     griddep_launch_dependents();
 
@@ -144,7 +155,10 @@ __global__ void __launch_bounds__(kLgThreads, 1)
             mbar_init(bar_full_b(s), 1);   // the loader thread (+ TMA bytes)
             mbar_init(bar_empty(s), 1);    // tcgen05.commit
         }
-        mbar_init(bar_acc, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_acc_full(b), 1);              // tcgen05.commit after a tile's last MMA
+            mbar_init(bar_acc_empty(b), kLgEpiWarps);   // the epilogue warps have read the buffer
+        }
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -154,7 +168,7 @@ __global__ void __launch_bounds__(kLgThreads, 1)
         const uint32_t v = reinterpret_cast<const uint32_t*>(rest + L::lut1)[i >> 3];
         sts128(lut_base + i * 16, make_uint4(v, v, v, v));
     }
-    if (warp == kLgDecoders + 1) tmem_alloc(sbase + L::tmem_slot, NT);
+    if (warp == kLgDecoders + 1) tmem_alloc(sbase + L::tmem_slot, 2 * NT);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -165,12 +179,17 @@ __global__ void __launch_bounds__(kLgThreads, 1)
         // ------------------------------------------------ activation loader
         if (lane == 0) {
             griddep_wait();  // the activations may come from the previous kernel
-            for (int ks = 0; ks < KS && ok; ++ks) {
-                const int s = ks % ST, it = ks / ST;
-                if (it > 0) ok = wait_or_abort(bar_empty(s), (it - 1) & 1, abort_flag);
-                if (!ok) break;
-                mbar_arrive_expect_tx(bar_full_b(s), NT * kLgKStep);
-                tma_load_2d(sbase + L::b + s * (NT * kLgKStep), &tmap_x, ks * kLgKStep, t0, bar_full_b(s));
+            int gs = 0;
+            for (int ti = 0; ti < my_tiles && ok; ++ti) {
+                const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+                const int t0 = (tile / RB) * NT;
+                for (int ks = 0; ks < KS; ++ks, ++gs) {
+                    const int s = gs % ST, it = gs / ST;
+                    if (it > 0) ok = wait_or_abort(bar_empty(s), (it - 1) & 1, abort_flag);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(bar_full_b(s), NT * kLgKStep);
+                    tma_load_2d(sbase + L::b + s * (NT * kLgKStep), &tmap_x, ks * kLgKStep, t0, bar_full_b(s));
+                }
             }
         }
     } else if (warp == kLgDecoders + 1) {
@@ -178,46 +197,61 @@ __global__ void __launch_bounds__(kLgThreads, 1)
         if (lane == 0) {
             // int8 x int8 -> int32, K-major A and B, M = 128, N = NT
             const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) | (8u << 24);
-            for (int ks = 0; ks < KS && ok; ++ks) {
-                const int s = ks % ST, it = ks / ST;
-                ok = wait_or_abort(bar_full_a(s), it & 1, abort_flag) && wait_or_abort(bar_full_b(s), it & 1, abort_flag);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t a_addr = sbase + L::a + s * kLgAStage, b_addr = sbase + L::b + s * (NT * kLgKStep);
+            int gs = 0;
+            for (int ti = 0; ti < my_tiles && ok; ++ti) {
+                const int buf = ti & 1, use = ti >> 1;
+                if (use > 0) {   // the epilogue must have drained this accumulator buffer
+                    ok = wait_or_abort(bar_acc_empty(buf), (use - 1) & 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                }
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * NT);
+                for (int ks = 0; ks < KS; ++ks, ++gs) {
+                    const int s = gs % ST, it = gs / ST;
+                    ok = wait_or_abort(bar_full_a(s), it & 1, abort_flag) &&
+                         wait_or_abort(bar_full_b(s), it & 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = sbase + L::a + s * kLgAStage, b_addr = sbase + L::b + s * (NT * kLgKStep);
 #pragma unroll
-                for (int j = 0; j < 4; ++j)   // four K=32 slices inside the 128-byte swizzle row
-                    umma_i8(tmem_base, umma_desc_sw128(a_addr + 32 * j), umma_desc_sw128(b_addr + 32 * j), idesc,
-                            (ks | j) != 0);
-                umma_commit(bar_empty(s));     // frees the stage when these MMAs have read it
+                    for (int j = 0; j < 4; ++j)   // four K=32 slices inside the 128-byte swizzle row
+                        umma_i8(d_tmem, umma_desc_sw128(a_addr + 32 * j), umma_desc_sw128(b_addr + 32 * j), idesc,
+                                (ks | j) != 0);
+                    umma_commit(bar_empty(s));     // frees the stage when these MMAs have read it
+                }
+                if (ok) umma_commit(bar_acc_full(buf));   // this tile's accumulators are complete
             }
-            umma_commit(bar_acc);              // accumulators complete
         }
-    } else {
+    } else if (warp < kLgDecoders) {
         // ---------------------------------------------------------- decoders
         const int sub = warp & 1, half = (warp >> 1) & 1, kk = (warp >> 2) & 1, grp = warp >> 3;
         const int g = lane >> 2, q = lane & 3;
-        const int rt = rb * 2 + half;
-        const bool have_rows = rt * 64 < N;
         const uint32_t lut_lane = lut_base | (uint32_t)(lane * 4);
-        // Register pipeline over this warp's tiles (k-steps grp, grp+2, ...):
-        //   stage A  bitmap words + offsets of the tile two steps ahead
-        //   stage B  sign-stream position and the eight sign words of the next tile
-        //   stage C  decode the current tile and store it
+        // Register pipeline over this warp's pipeline steps gs = grp, grp+2, ... (numbered through
+        // all tiles of the CTA, so it runs ahead across tile boundaries):
+        //   stage A  bitmap words + offsets of the step two ahead
+        //   stage B  sign-stream position and the sign words of the next step
+        //   stage C  decode the current step and store it
         // so the three dependent global round trips of a tile overlap the
         // decoding of the two tiles before it.
         struct Head { uint4 bw; int toff, qbase; bool valid; };
         struct Signs { uint32_t lo[2], hi[2], sh[2]; };   // this warp's two bitmap words: 2*sub, 2*sub+1
-        auto load_head = [&](int ks) {
+        auto load_head = [&](int gs) {
             Head h;
-            const int kt = ks * 2 + kk;
-            h.valid = have_rows && ks < KS && kt < KT;
+            h.valid = false;
             h.bw = make_uint4(0, 0, 0, 0), h.toff = 0, h.qbase = 0;
-            if (h.valid) {
-                const long long T = (long long)rt * KT + kt;
-                h.bw = __ldg(reinterpret_cast<const uint4*>(p.bitmap + T * 128) + lane);
-                h.toff = __ldg(p.tile_off + T);
-                const int qd = lane >> 3;
-                h.qbase = qd ? (int)__ldg(p.quarter_off + 3 * T + qd - 1) : 0;
+            if (gs < G) {
+                const int ti = gs / KS, ks = gs - ti * KS;
+                const int rt = (((int)blockIdx.x + ti * (int)gridDim.x) % RB) * 2 + half;
+                const int kt = ks * 2 + kk;
+                h.valid = rt * 64 < N && kt < KT;
+                if (h.valid) {
+                    const long long T = (long long)rt * KT + kt;
+                    h.bw = __ldg(reinterpret_cast<const uint4*>(p.bitmap + T * 128) + lane);
+                    h.toff = __ldg(p.tile_off + T);
+                    const int qd = lane >> 3;
+                    h.qbase = qd ? (int)__ldg(p.quarter_off + 3 * T + qd - 1) : 0;
+                }
             }
             return h;
         };
@@ -248,9 +282,9 @@ __global__ void __launch_bounds__(kLgThreads, 1)
         };
         Head h_cur = load_head(grp), h_nxt = load_head(grp + 2);
         Signs s_cur = load_signs(h_cur);
-        for (int ks = grp; ks < KS && ok; ks += 2) {
-            const int s = ks % ST, it = ks / ST;
-            const Head h_far = load_head(ks + 4);      // stage A
+        for (int gs = grp; gs < G && ok; gs += 2) {
+            const int s = gs % ST, it = gs / ST;
+            const Head h_far = load_head(gs + 4);      // stage A
             const Signs s_nxt = load_signs(h_nxt);     // stage B
             if (it > 0) ok = wait_or_abort(bar_empty(s), (it - 1) & 1, abort_flag);
             if (!ok) break;
@@ -275,44 +309,87 @@ __global__ void __launch_bounds__(kLgThreads, 1)
             if (lane == 0) mbar_arrive(bar_full_a(s));
             h_cur = h_nxt, h_nxt = h_far, s_cur = s_nxt;
         }
-
+    } else {
         // ---------------------------------------------------------- epilogue
-        griddep_wait();  // scales and the output buffer may belong to the previous kernel
-        const int dtid = tid;  // 0..255
-        if (p.epilogue != EPI_RAW_I32)
-            for (int i = dtid; i < NT; i += kLgDecoders * 32) s_s[i] = (t0 + i < M) ? __bfloat162float(p.s[t0 + i]) : 1.f;
-        asm volatile("bar.sync 1, %0;" ::"n"(kLgDecoders * 32) : "memory");
-        if (ok) ok = wait_or_abort(bar_acc, 0, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);   // the tensor-memory loads below are warp-collective
-        tc_fence_after();
-        const int quarter = warp & 3, cpart = warp >> 2;   // TMEM lane quarter (= warp % 4) and column quarter
-        const int n = rb * 128 + 32 * quarter + lane;
-        const bool n_ok = n < N;
-        float ws_el = 0.f;
-        if (p.epilogue != EPI_RAW_I32 && p.epilogue != EPI_F32_DIV && n_ok)
-            ws_el = __bfloat162float(p.ws[ws_group(n, p)]);
-        if (ok) {
+        griddep_wait();  // scales, residual and the output buffer may belong to the previous kernel
+        const int quarter = warp & 3;          // the tensor-memory lanes a warp may read: 32 * (warp % 4)
+        constexpr int CW = NT / 2;             // token columns per epilogue warp
+        const int cb = ((warp - (kLgDecoders + 2)) >> 2) * CW;
+        float* s_w = s_s + (warp - (kLgDecoders + 2)) * CW;   // this warp's scales (or coefficients) of the tile
+        for (int ti = 0; ti < my_tiles; ++ti) {
+            const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+            const int rb = tile % RB, t0 = (tile / RB) * NT + cb;
+            const int buf = ti & 1, use = ti >> 1;
+            const int n = rb * 128 + 32 * quarter + lane;
+            const bool n_ok = n < N;
+            const bool scaled = p.epilogue == EPI_DECODE || p.epilogue == EPI_PREFILL;
+            const int gsel = (scaled && n_ok) ? ws_group(n, p) : -1;
+            const float ws_el = gsel >= 0 ? __bfloat162float(p.ws[gsel]) : 0.f;
+            // Prefill form with one scale segment for all 32 rows of the warp (always, under the
+            // reference's per-128-column rule): the coefficient ws/s[t] is formed once per token
+            // and the per-element work is one multiply.
+            const int g0 = __shfl_sync(0xffffffffu, gsel, 0);
+            const bool fast = p.epilogue == EPI_PREFILL && __all_sync(0xffffffffu, gsel == g0 || gsel < 0);
+            const float ws0 = __shfl_sync(0xffffffffu, ws_el, 0);
+            __syncwarp();                          // the previous tile's scales are no longer read
+            if (p.epilogue != EPI_RAW_I32)
+                for (int i = lane; i < CW; i += 32) {
+                    const float sv = (t0 + i < M) ? __bfloat162float(p.s[t0 + i]) : 1.f;
+                    s_w[i] = fast ? ((sv != 0.f) ? __fdiv_rn(ws0, sv) : 0.f) : sv;
+                }
+            __syncwarp();
+            if (ok) ok = wait_or_abort(bar_acc_full(buf), use & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);   // the tensor-memory loads below are warp-collective
+            if (!ok) break;
+            tc_fence_after();
+            const int cols = min(CW, M - t0);   // live tokens of this warp's columns
 #pragma unroll 1
-            for (int c0 = cpart * (NT / 4); c0 < (cpart + 1) * (NT / 4); c0 += 16) {
+            for (int c0 = 0; c0 < cols; c0 += 16) {
+                // All loads of a 16-token slice (tensor memory, scales, residual) are issued before
+                // its first store: the output pointer is generic, so a store in between would order
+                // every later load behind it and serialise the slice.
                 int v[16];
-                tmem_ld16(tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)c0, v);
+                float sc[16];
+                tmem_ld16(tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(buf * NT + cb + c0), v);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int t = t0 + c0 + j;
-                    if (n_ok && t < M) {
-                        const long long o = (long long)t * N + n;
-                        if (p.epilogue == EPI_RAW_I32) reinterpret_cast<int*>(p.out)[o] = v[j];
-                        else if (p.epilogue == EPI_F32_DIV) reinterpret_cast<float*>(p.out)[o] = __fdiv_rn(__int2float_rn(v[j]), s_s[c0 + j]);
-                        else reinterpret_cast<__nv_bfloat16*>(p.out)[o] = add_residual(scale_epilogue(v[j], s_s[c0 + j], ws_el, p.epilogue), p.residual, o);
+                for (int j = 0; j < 16; ++j) sc[j] = s_w[c0 + j];
+                const long long o0 = (long long)(t0 + c0) * N + n;
+                const int live = n_ok ? min(16, M - t0 - c0) : 0;
+                if (p.epilogue == EPI_RAW_I32) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (j < live) reinterpret_cast<int*>(p.out)[o0 + (long long)j * N] = v[j];
+                } else if (p.epilogue == EPI_F32_DIV) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (j < live) reinterpret_cast<float*>(p.out)[o0 + (long long)j * N] = __fdiv_rn(__int2float_rn(v[j]), sc[j]);
+                } else {
+                    __nv_bfloat16 r[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        r[j] = fast ? __float2bfloat16_rn(__fmul_rn(__int2float_rn(v[j]), sc[j]))
+                                    : scale_epilogue(v[j], sc[j], ws_el, p.epilogue);
+                    if (p.residual) {
+                        __nv_bfloat16 res[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) res[j] = j < live ? p.residual[o0 + (long long)j * N] : r[j];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) r[j] = __float2bfloat16_rn(__bfloat162float(res[j]) + __bfloat162float(r[j]));
                     }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (j < live) reinterpret_cast<__nv_bfloat16*>(p.out)[o0 + (long long)j * N] = r[j];
                 }
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty(buf));   // the MMA warp may overwrite this buffer
         }
     }
     if (*abort_flag && tid == 0) atomicExch(p.status, ST_WAIT_TIMEOUT);
     tc_fence_before();
     __syncthreads();
-    if (warp == kLgDecoders + 1) tmem_dealloc(tmem_base, NT);
+    if (warp == kLgDecoders + 1) tmem_dealloc(tmem_base, 2 * NT);
 }
 
 }  // namespace tsp

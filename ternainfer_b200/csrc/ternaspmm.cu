@@ -10,6 +10,8 @@
 #include <limits.h>
 #include <stdlib.h>
 
+#include <algorithm>
+
 #include "act_quant.cuh"
 #include "spmm_large_m.cuh"
 #include "spmm_small_m.cuh"
@@ -177,7 +179,8 @@ static cudaError_t launch_large_m(const SpmmParams& p, cudaStream_t stream) {
     CUtensorMap map;
     if (!encode_x_map(&map, p.x, p.M, p.K, NT)) return cudaErrorInvalidValue;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((p.N + 127) / 128, (p.M + NT - 1) / NT, 1);
+    const long long tiles = (long long)((p.N + 127) / 128) * ((p.M + NT - 1) / NT);
+    cfg.gridDim = dim3((unsigned)std::min<long long>(tiles, device_sm_count()), 1, 1);   // persistent: one CTA per SM
     cfg.blockDim = dim3(kLgThreads, 1, 1);
     cfg.dynamicSmemBytes = L::total;
     cfg.stream = stream;

@@ -283,3 +283,22 @@ def test_full_size_prefill_against_c_oracle(lib):
     assert (accumulate(lib, xq, pk) == acc).all()
     got = call(lib, "bitlinear_TernaSpMM", xq, pk, sb, wb, 2)
     assert (got == want).all()
+
+
+
+
+@pytest.mark.parametrize("M,N,K", [(600, 13888, 320), (1030, 9536, 192), (100, 38464, 128), (40, 38464, 192)])
+def test_persistent_ctas_with_several_tiles_each(lib, M, N, K):
+    """More output tiles than SMs, so every CTA of the tensor-core kernel walks through several
+    tiles and both accumulator buffers of tensor memory are reused; ragged last token tile and a
+    last row block of 64 rows.  Accumulators bit-exact against the C oracle, bf16 identical."""
+    w = o.make_ternary(N, K, 0.45, seed=M)
+    xq, s = o.make_activations(M, K, seed=M + 1)
+    ws = o.make_ws(2, seed=M + 2)
+    sb, wb = o.f32_to_bf16_bits(s.reshape(-1)), o.f32_to_bf16_bits(ws)
+    pk = Packed(w)
+    acc, want = c_oracle.ternaspmm(xq, w, sb, wb, 2)
+    assert (accumulate(lib, xq, pk) == acc).all()
+    got = call(lib, "bitlinear_TernaSpMM", xq, pk, sb, wb, 2)
+    assert lib.ternaspmm_last_status() == 0
+    assert (got == want).all()
