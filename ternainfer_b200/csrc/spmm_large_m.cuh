@@ -13,20 +13,21 @@
 // MMA's M) x NT tokens (the MMA's N); a tile runs over all of K in pipeline
 // steps of 128 k.  Tensor memory holds TWO accumulator buffers of NT columns,
 // so the epilogue of tile i overlaps the K loop of tile i+1.  Warp roles:
-//   warps 0-15 decoders: two warps share the 64x64 weight tile (row half,
-//              k half) of every second k-step, each taking two of the four
-//              16-row groups; they read bitmaps, offsets and sign words from
-//              global memory through a register pipeline that runs ahead
-//              across tile boundaries, decode with the same table lookup as
-//              the small-batch kernel and store int8 rows of 128 k in the
-//              128-byte-swizzled K-major layout.
-//   warp 16    activation loader: one thread issues 2-D TMA tile loads of
+//   warp 0     activation loader: one thread issues 2-D TMA tile loads of
 //              x[NT tokens][128 k] (128-byte swizzle, no multicast).
-//   warp 17    one thread issues tcgen05.mma (four K=32 steps per stage) and
+//   warp 1     one thread issues tcgen05.mma (four K=32 steps per stage) and
 //              commits stage releases / the accumulator-full barrier.
-//   warps 18-25 epilogue: tcgen05.ld of one 32-lane quarter and one half of
+//   warps 2-9  epilogue: tcgen05.ld of one 32-lane quarter and one half of
 //              the token columns each -> scale -> bf16 (or int32 / fp32)
 //              stores, then hand the buffer back.
+//   warps 10.. decoders, four per pipeline stage: decoder group g owns stage g
+//              and handles every k-step gs with gs % stages == g; each of its
+//              warps takes one 64x64 tile of the packed format (row half, k
+//              half).  They read bitmaps, offsets and sign words from global
+//              memory through a register pipeline that runs ahead across tile
+//              boundaries, decode with the same table lookup as the
+//              small-batch kernel and store int8 rows of 128 k in the
+//              128-byte-swizzled K-major layout.
 // All hand-offs are mbarriers; every wait has an iteration limit and a CTA-wide
 // abort flag so that a lost signal ends the kernel with a status word.
 #pragma once
@@ -36,15 +37,16 @@
 
 namespace tsp {
 
-constexpr int kLgDecoders = 16;          // two warps per 64x64 tile, two k-steps in flight
 constexpr int kLgEpiWarps = 8;           // two per 32-lane quarter of tensor memory, half of the token columns each
-constexpr int kLgThreads = (kLgDecoders + 2 + kLgEpiWarps) * 32;
+constexpr int kLgFirstEpi = 2;           // warp 0 loads activations, warp 1 issues the MMAs
+constexpr int kLgFirstDecoder = kLgFirstEpi + kLgEpiWarps;
 constexpr int kLgKStep = 128;            // k per pipeline stage = one 128-byte swizzle row
 constexpr int kLgAStage = 128 * 128;     // bytes: 128 rows x 128 k int8
 
 template <int NT>
 struct LargeMSmem {
     static constexpr int stages = NT > 128 ? 3 : 4;
+    static constexpr int threads = (kLgFirstDecoder + 4 * stages) * 32;   // four decoder warps per stage
     static constexpr int bars = 0;                         // full_a[4] full_b[4] empty[4] acc_full[2] acc_empty[2]
     static constexpr int tmem_slot = 136;
     static constexpr int abort_flag = 140;
@@ -118,7 +120,7 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
 }
 
 template <int NT>
-__global__ void __launch_bounds__(kLgThreads, 1)
+__global__ void __launch_bounds__(LargeMSmem<NT>::threads, 1)
     spmm_large_m_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap tmap_x) {
     using L = LargeMSmem<NT>;
     constexpr int ST = L::stages;
@@ -151,7 +153,7 @@ __global__ void __launch_bounds__(kLgThreads, 1)
     // ---- set-up
     if (tid == 0) {
         for (int s = 0; s < 4; ++s) {
-            mbar_init(bar_full_a(s), 8);   // the eight decoder warps of a stage
+            mbar_init(bar_full_a(s), 4);   // the four decoder warps of a stage
             mbar_init(bar_full_b(s), 1);   // the loader thread (+ TMA bytes)
             mbar_init(bar_empty(s), 1);    // tcgen05.commit
         }
@@ -162,20 +164,20 @@ __global__ void __launch_bounds__(kLgThreads, 1)
         *abort_flag = 0;
         mbar_fence_init();
     }
-    for (int e = tid; e < 256; e += kLgThreads) reinterpret_cast<uint32_t*>(rest + L::lut1)[e] = lut_entry(e);
+    for (int e = tid; e < 256; e += L::threads) reinterpret_cast<uint32_t*>(rest + L::lut1)[e] = lut_entry(e);
     __syncthreads();
-    for (int i = tid; i < 256 * 8; i += kLgThreads) {
+    for (int i = tid; i < 256 * 8; i += L::threads) {
         const uint32_t v = reinterpret_cast<const uint32_t*>(rest + L::lut1)[i >> 3];
         sts128(lut_base + i * 16, make_uint4(v, v, v, v));
     }
-    if (warp == kLgDecoders + 1) tmem_alloc(sbase + L::tmem_slot, 2 * NT);
+    if (warp == 1) tmem_alloc(sbase + L::tmem_slot, 2 * NT);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(rest + L::tmem_slot);
     bool ok = true;
 
-    if (warp == kLgDecoders) {
+    if (warp == 0) {
         // ------------------------------------------------ activation loader
         if (lane == 0) {
             griddep_wait();  // the activations may come from the previous kernel
@@ -192,7 +194,7 @@ __global__ void __launch_bounds__(kLgThreads, 1)
                 }
             }
         }
-    } else if (warp == kLgDecoders + 1) {
+    } else if (warp == 1) {
         // ------------------------------------------------------ MMA issuer
         if (lane == 0) {
             // int8 x int8 -> int32, K-major A and B, M = 128, N = NT
@@ -222,100 +224,73 @@ __global__ void __launch_bounds__(kLgThreads, 1)
                 if (ok) umma_commit(bar_acc_full(buf));   // this tile's accumulators are complete
             }
         }
-    } else if (warp < kLgDecoders) {
+    } else if (warp >= kLgFirstDecoder) {
         // ---------------------------------------------------------- decoders
-        const int sub = warp & 1, half = (warp >> 1) & 1, kk = (warp >> 2) & 1, grp = warp >> 3;
+        const int dw = warp - kLgFirstDecoder;
+        const int half = dw & 1, kk = (dw >> 1) & 1, grp = dw >> 2;   // grp = the pipeline stage this group owns
         const int g = lane >> 2, q = lane & 3;
         const uint32_t lut_lane = lut_base | (uint32_t)(lane * 4);
-        // Register pipeline over this warp's pipeline steps gs = grp, grp+2, ... (numbered through
-        // all tiles of the CTA, so it runs ahead across tile boundaries):
+        const int steps = G > grp ? (G - grp + ST - 1) / ST : 0;      // this group's pipeline steps grp, grp+ST, ...
+        // Register pipeline over those steps (it runs ahead across tile boundaries):
         //   stage A  bitmap words + offsets of the step two ahead
         //   stage B  sign-stream position and the sign words of the next step
         //   stage C  decode the current step and store it
-        // so the three dependent global round trips of a tile overlap the
-        // decoding of the two tiles before it.
-        struct Head { uint4 bw; int toff, qbase; bool valid; };
-        struct Signs { uint32_t lo[2], hi[2], sh[2]; };   // this warp's two bitmap words: 2*sub, 2*sub+1
-        auto load_head = [&](int gs) {
-            Head h;
-            h.valid = false;
-            h.bw = make_uint4(0, 0, 0, 0), h.toff = 0, h.qbase = 0;
-            if (gs < G) {
-                const int ti = gs / KS, ks = gs - ti * KS;
-                const int rt = (((int)blockIdx.x + ti * (int)gridDim.x) % RB) * 2 + half;
-                const int kt = ks * 2 + kk;
-                h.valid = rt * 64 < N && kt < KT;
-                if (h.valid) {
-                    const long long T = (long long)rt * KT + kt;
-                    h.bw = __ldg(reinterpret_cast<const uint4*>(p.bitmap + T * 128) + lane);
-                    h.toff = __ldg(p.tile_off + T);
-                    const int qd = lane >> 3;
-                    h.qbase = qd ? (int)__ldg(p.quarter_off + 3 * T + qd - 1) : 0;
-                }
+        // so the three dependent global round trips of a tile overlap the decoding of the
+        // two tiles before it.  (row block, k-step) of the step whose head is loaded next
+        // advance incrementally - no division in the loop.
+        int f_ks = grp, f_rb = (int)(blockIdx.x % (unsigned)RB), f_left = my_tiles;
+        const int rb_step = (int)(gridDim.x % (unsigned)RB);
+        bool f_valid;
+        auto next_head = [&]() {
+            while (f_left > 0 && f_ks >= KS) {
+                f_ks -= KS, --f_left;
+                f_rb += rb_step;
+                if (f_rb >= RB) f_rb -= RB;
             }
-            return h;
+            const int rt = f_rb * 2 + half, kt = f_ks * 2 + kk;
+            f_valid = f_left > 0 && rt * 64 < N && kt < KT;
+            f_ks += ST;
+            return load_head(p, (long long)rt * KT + kt, f_valid, lane);
         };
-        auto load_signs = [&](const Head& h) {
-            Signs sg;
-            const uint32_t w[4] = {h.bw.x, h.bw.y, h.bw.z, h.bw.w};
-            int cnt[4];
-#pragma unroll
-            for (int r = 0; r < 4; ++r) cnt[r] = __popc(w[r]);
-            const int tot = cnt[0] + cnt[1] + cnt[2] + cnt[3];
-            int incl = tot;
-#pragma unroll
-            for (int d = 1; d < 8; d <<= 1) {
-                const int t = __shfl_up_sync(0xffffffffu, incl, d, 8);
-                if ((lane & 7) >= d) incl += t;
-            }
-            long long pos = (long long)h.toff + h.qbase + incl - tot + (sub ? cnt[0] + cnt[1] : 0);
-            const int mine[2] = {sub ? cnt[2] : cnt[0], sub ? cnt[3] : cnt[1]};
-#pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                const uint32_t* sw = p.signs + (pos >> 5);
-                sg.lo[r] = h.valid ? __ldg(sw) : 0u;
-                sg.hi[r] = h.valid ? __ldg(sw + 1) : 0u;
-                sg.sh[r] = (uint32_t)pos & 31u;
-                pos += mine[r];
-            }
-            return sg;
-        };
-        Head h_cur = load_head(grp), h_nxt = load_head(grp + 2);
-        Signs s_cur = load_signs(h_cur);
-        for (int gs = grp; gs < G && ok; gs += 2) {
-            const int s = gs % ST, it = gs / ST;
-            const Head h_far = load_head(gs + 4);      // stage A
-            const Signs s_nxt = load_signs(h_nxt);     // stage B
-            if (it > 0) ok = wait_or_abort(bar_empty(s), (it - 1) & 1, abort_flag);
+        TileHead h_cur = next_head();
+        bool v_cur = f_valid;
+        TileHead h_nxt = next_head();
+        bool v_nxt = f_valid;
+        TileSigns s_cur = load_signs(p, h_cur, v_cur, lane);
+        const uint32_t a_stage = sbase + L::a + grp * kLgAStage;
+        // row = 64*half + 16*r + 8*h + g (row & 7 == g), 16-byte chunk (4*kk + q) ^ g: 128-byte swizzle
+        const uint32_t a_lane = a_stage + (uint32_t)((64 * half + g) * 128) + (((uint32_t)(4 * kk + q) ^ (uint32_t)g) << 4);
+        for (int i = 0; i < steps && ok; ++i) {
+            const TileHead h_far = next_head();                       // stage A
+            const bool v_far = f_valid;
+            const TileSigns s_nxt = load_signs(p, h_nxt, v_nxt, lane);   // stage B
+            if (i > 0) ok = wait_or_abort(bar_empty(grp), (i - 1) & 1, abort_flag);
             if (!ok) break;
-            if (h_cur.valid) {                         // stage C
-                const uint32_t w[2] = {sub ? h_cur.bw.z : h_cur.bw.x, sub ? h_cur.bw.w : h_cur.bw.y};
-                const uint32_t a_stage = sbase + L::a + s * kLgAStage;
+            if (v_cur) {                                              // stage C
+                const uint32_t w[4] = {h_cur.bw.x, h_cur.bw.y, h_cur.bw.z, h_cur.bw.w};
+                int pos = s_cur.pos;
 #pragma unroll
-                for (int rr = 0; rr < 2; ++rr) {
-                    const int r = 2 * sub + rr;
+                for (int r = 0; r < 4; ++r) {
                     uint32_t a[8];
-                    decode_word(w[rr], __funnelshift_r(s_cur.lo[rr], s_cur.hi[rr], s_cur.sh[rr]), lut_lane, a);
+                    decode_word(w[r], __funnelshift_r(s_cur.lo[r], s_cur.hi[r], (uint32_t)pos), lut_lane, a);
+                    pos += __popc(w[r]);
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const int row = 64 * half + 16 * r + 8 * h + g;          // row & 7 == g
-                        const uint32_t chunk = (uint32_t)((4 * kk + q) ^ g);     // 128-byte swizzle
-                        sts128(a_stage + row * 128 + chunk * 16, make_uint4(a[h], a[2 + h], a[4 + h], a[6 + h]));
-                    }
+                    for (int h = 0; h < 2; ++h)
+                        sts128(a_lane + (uint32_t)((16 * r + 8 * h) * 128), make_uint4(a[h], a[2 + h], a[4 + h], a[6 + h]));
                 }
             }
             fence_proxy_async_smem();   // generic-proxy stores -> visible to the tensor core's async proxy
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_full_a(s));
-            h_cur = h_nxt, h_nxt = h_far, s_cur = s_nxt;
+            if (lane == 0) mbar_arrive(bar_full_a(grp));
+            h_cur = h_nxt, v_cur = v_nxt, h_nxt = h_far, v_nxt = v_far, s_cur = s_nxt;
         }
     } else {
         // ---------------------------------------------------------- epilogue
         griddep_wait();  // scales, residual and the output buffer may belong to the previous kernel
         const int quarter = warp & 3;          // the tensor-memory lanes a warp may read: 32 * (warp % 4)
         constexpr int CW = NT / 2;             // token columns per epilogue warp
-        const int cb = ((warp - (kLgDecoders + 2)) >> 2) * CW;
-        float* s_w = s_s + (warp - (kLgDecoders + 2)) * CW;   // this warp's scales (or coefficients) of the tile
+        const int cb = ((warp - kLgFirstEpi) >> 2) * CW;
+        float* s_w = s_s + (warp - kLgFirstEpi) * CW;   // this warp's scales (or coefficients) of the tile
         for (int ti = 0; ti < my_tiles; ++ti) {
             const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
             const int rb = tile % RB, t0 = (tile / RB) * NT + cb;
@@ -389,7 +364,7 @@ __global__ void __launch_bounds__(kLgThreads, 1)
     if (*abort_flag && tid == 0) atomicExch(p.status, ST_WAIT_TIMEOUT);
     tc_fence_before();
     __syncthreads();
-    if (warp == kLgDecoders + 1) tmem_dealloc(tmem_base, 2 * NT);
+    if (warp == 1) tmem_dealloc(tmem_base, 2 * NT);
 }
 
 }  // namespace tsp

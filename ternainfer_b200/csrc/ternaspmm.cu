@@ -181,7 +181,7 @@ static cudaError_t launch_large_m(const SpmmParams& p, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
     const long long tiles = (long long)((p.N + 127) / 128) * ((p.M + NT - 1) / NT);
     cfg.gridDim = dim3((unsigned)std::min<long long>(tiles, device_sm_count()), 1, 1);   // persistent: one CTA per SM
-    cfg.blockDim = dim3(kLgThreads, 1, 1);
+    cfg.blockDim = dim3(L::threads, 1, 1);
     cfg.dynamicSmemBytes = L::total;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
