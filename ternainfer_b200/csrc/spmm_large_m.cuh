@@ -30,6 +30,17 @@
 //              128-byte-swizzled K-major layout.
 // All hand-offs are mbarriers; every wait has an iteration limit and a CTA-wide
 // abort flag so that a lost signal ends the kernel with a status word.
+//
+// K split.  A launch with fewer output tiles than half the SMs (narrow layers
+// at a few hundred tokens, the K-sharded linears of a big model) would leave
+// most of the chip idle while each CTA walks through all of K.  Such launches
+// run as thread-block clusters of S = 2, 4 or 8 CTAs per tile: CTA r takes the
+// r-th slice of K, and the partial accumulators are reduce-scattered through
+// distributed shared memory - every CTA owns NT/S token columns, receives the
+// other CTAs' partials for them as 16-byte st.shared::cluster stores into one
+// slot per sender of the (by then idle) pipeline stage memory, adds them to
+// its own accumulators and runs the epilogue for its columns.  (Remote
+// atomics were measured at 1-2 per clock per SM and are not used here.)
 #pragma once
 #include <cuda.h>
 
@@ -145,9 +156,16 @@ __global__ void __launch_bounds__(LargeMSmem<NT>::threads, 1)
     // side by side share the activation tile in L2.
     const int RB = (N + 127) / 128;
     const int n_tiles = RB * ((M + NT - 1) / NT);
-    const int my_tiles = ((int)blockIdx.x < n_tiles) ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-    const int G = my_tiles * KS;           // pipeline steps of this CTA over all its tiles
+    // K split: the S CTAs of a cluster share a tile; CTA `crank` takes k-steps [ks0, ks0 + KSl).
+    // Without a split the "cluster" is the CTA itself.
+    const int S = p.splits;
+    const int cid = (int)blockIdx.x / S, ncl = (int)gridDim.x / S, crank = (int)blockIdx.x - cid * S;
+    const int ks0 = (int)(((long long)KS * crank) / S);
+    const int KSl = (int)(((long long)KS * (crank + 1)) / S) - ks0;
+    const int my_tiles = (cid < n_tiles) ? (n_tiles - 1 - cid) / ncl + 1 : 0;   // exactly 1 when S > 1
+    const int G = my_tiles * KSl;          // pipeline steps of this CTA over all its tiles
 
+    phase_mark(0);
     griddep_launch_dependents();
 
     // ---- set-up
@@ -176,6 +194,7 @@ __global__ void __launch_bounds__(LargeMSmem<NT>::threads, 1)
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(rest + L::tmem_slot);
     bool ok = true;
+    phase_mark(1);
 
     if (warp == 0) {
         // ------------------------------------------------ activation loader
@@ -183,9 +202,9 @@ __global__ void __launch_bounds__(LargeMSmem<NT>::threads, 1)
             griddep_wait();  // the activations may come from the previous kernel
             int gs = 0;
             for (int ti = 0; ti < my_tiles && ok; ++ti) {
-                const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+                const int tile = cid + ti * ncl;
                 const int t0 = (tile / RB) * NT;
-                for (int ks = 0; ks < KS; ++ks, ++gs) {
+                for (int ks = ks0; ks < ks0 + KSl; ++ks, ++gs) {
                     const int s = gs % ST, it = gs / ST;
                     if (it > 0) ok = wait_or_abort(bar_empty(s), (it - 1) & 1, abort_flag);
                     if (!ok) break;
@@ -208,12 +227,13 @@ __global__ void __launch_bounds__(LargeMSmem<NT>::threads, 1)
                     tc_fence_after();
                 }
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * NT);
-                for (int ks = 0; ks < KS; ++ks, ++gs) {
+                for (int ks = 0; ks < KSl; ++ks, ++gs) {
                     const int s = gs % ST, it = gs / ST;
                     ok = wait_or_abort(bar_full_a(s), it & 1, abort_flag) &&
                          wait_or_abort(bar_full_b(s), it & 1, abort_flag);
                     if (!ok) break;
                     tc_fence_after();
+                    if (gs == 0) phase_mark_here(2);
                     const uint32_t a_addr = sbase + L::a + s * kLgAStage, b_addr = sbase + L::b + s * (NT * kLgKStep);
 #pragma unroll
                     for (int j = 0; j < 4; ++j)   // four K=32 slices inside the 128-byte swizzle row
@@ -223,6 +243,7 @@ __global__ void __launch_bounds__(LargeMSmem<NT>::threads, 1)
                 }
                 if (ok) umma_commit(bar_acc_full(buf));   // this tile's accumulators are complete
             }
+            phase_mark_here(3);
         }
     } else if (warp >= kLgFirstDecoder) {
         // ---------------------------------------------------------- decoders
@@ -238,16 +259,16 @@ __global__ void __launch_bounds__(LargeMSmem<NT>::threads, 1)
         // so the three dependent global round trips of a tile overlap the decoding of the
         // two tiles before it.  (row block, k-step) of the step whose head is loaded next
         // advance incrementally - no division in the loop.
-        int f_ks = grp, f_rb = (int)(blockIdx.x % (unsigned)RB), f_left = my_tiles;
-        const int rb_step = (int)(gridDim.x % (unsigned)RB);
+        int f_ks = grp, f_rb = cid % RB, f_left = my_tiles;
+        const int rb_step = ncl % RB;
         bool f_valid;
         auto next_head = [&]() {
-            while (f_left > 0 && f_ks >= KS) {
-                f_ks -= KS, --f_left;
+            while (f_left > 0 && f_ks >= KSl) {
+                f_ks -= KSl, --f_left;
                 f_rb += rb_step;
                 if (f_rb >= RB) f_rb -= RB;
             }
-            const int rt = f_rb * 2 + half, kt = f_ks * 2 + kk;
+            const int rt = f_rb * 2 + half, kt = (ks0 + f_ks) * 2 + kk;
             f_valid = f_left > 0 && rt * 64 < N && kt < KT;
             f_ks += ST;
             return load_head(p, (long long)rt * KT + kt, f_valid, lane);
@@ -291,8 +312,8 @@ __global__ void __launch_bounds__(LargeMSmem<NT>::threads, 1)
         constexpr int CW = NT / 2;             // token columns per epilogue warp
         const int cb = ((warp - kLgFirstEpi) >> 2) * CW;
         float* s_w = s_s + (warp - kLgFirstEpi) * CW;   // this warp's scales (or coefficients) of the tile
-        for (int ti = 0; ti < my_tiles; ++ti) {
-            const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+        for (int ti = 0; ti < (S == 1 ? my_tiles : 0); ++ti) {
+            const int tile = cid + ti * ncl;
             const int rb = tile % RB, t0 = (tile / RB) * NT + cb;
             const int buf = ti & 1, use = ti >> 1;
             const int n = rb * 128 + 32 * quarter + lane;
@@ -361,9 +382,121 @@ __global__ void __launch_bounds__(LargeMSmem<NT>::threads, 1)
             if (lane == 0) mbar_arrive(bar_acc_empty(buf));   // the MMA warp may overwrite this buffer
         }
     }
+    if (S > 1) {
+        // K split: reduce-scatter of the partial accumulators over the cluster.  Everything else of the
+        // CTA is idle by now, so 16 warps take part (the eight epilogue warps and the first eight decoder
+        // warps: four per 32-lane quarter of tensor memory); all threads pass the two cluster barriers.
+        const bool helper = warp >= kLgFirstEpi && warp < kLgFirstEpi + 16 && my_tiles > 0;
+        const int quarter = warp & 3, part = (warp - kLgFirstEpi) >> 2;   // part 0..3 of the columns
+        const int row = 32 * quarter + lane;
+        const int CWo = NT / S;                            // token columns per owner, a power of two >= 16
+        const int lg = 31 - __clz(CWo);
+        const int SLOT = CWo * 128 * 4;                    // bytes per sender: [CWo/4 column groups][128 rows][4 columns]
+        const int rb = cid % RB, t0 = (cid / RB) * NT;
+        const uint32_t buf = sbase + L::a;                 // S-1 slots, one per sending CTA
+        const int per = CWo / 4;                           // owned columns finished by this warp (>= 4)
+        const int tb = t0 + crank * CWo + part * per;      // its first token
+        const int n = rb * 128 + row;
+        const bool n_ok = n < N;
+        float* s_w = s_s + (warp - kLgFirstEpi) * (NT / 8);
+        bool fast = false;
+        float ws_el = 0.f;
+        if (helper) {
+            // step 1: scales (or prefill coefficients ws/s) of the columns this warp will finish, then wait
+            // until this CTA's accumulators are complete - its stage memory is idle from then on
+            griddep_wait();
+            const bool scaled = p.epilogue == EPI_DECODE || p.epilogue == EPI_PREFILL;
+            const int gsel = (scaled && n_ok) ? ws_group(n, p) : -1;
+            ws_el = gsel >= 0 ? __bfloat162float(p.ws[gsel]) : 0.f;
+            const int g0 = __shfl_sync(0xffffffffu, gsel, 0);
+            fast = p.epilogue == EPI_PREFILL && __all_sync(0xffffffffu, gsel == g0 || gsel < 0);
+            const float ws0 = __shfl_sync(0xffffffffu, ws_el, 0);
+            if (p.epilogue != EPI_RAW_I32)
+                for (int i = lane; i < per; i += 32) {
+                    const float sv = (tb + i < M) ? __bfloat162float(p.s[tb + i]) : 1.f;
+                    s_w[i] = fast ? ((sv != 0.f) ? __fdiv_rn(ws0, sv) : 0.f) : sv;
+                }
+            __syncwarp();
+            if (ok) ok = wait_or_abort(bar_acc_full(0), 0, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            tc_fence_after();
+            if (tid == kLgFirstEpi * 32) phase_mark_here(4);
+        }
+        __syncwarp();
+        cluster_arrive();
+        cluster_wait();                                    // every CTA of the cluster is done with its stage memory
+        phase_mark(5);
+        if (helper && ok) {
+            // step 2: send the partial accumulators of foreign columns to their owners, 4 columns per store
+            const int live = min(NT, M - t0);
+            for (int c0 = part * (NT / 4); c0 < min((part + 1) * (NT / 4), live); c0 += 16) {
+                const int owner = c0 >> lg;                // a 16-column slice has one owner
+                if (owner == crank) continue;
+                int v[16];
+                tmem_ld16(tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)c0, v);
+                const int slot = crank < owner ? crank : crank - 1;
+                // a warp's 32 rows of one column group are 512 contiguous bytes
+                const uint32_t dst = map_to_rank(buf + (uint32_t)(slot * SLOT + ((((c0 & (CWo - 1)) >> 2) * 128 + row) << 4)),
+                                                 (uint32_t)owner);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (c0 + 4 * i < live) st_cluster_v4(dst + 2048 * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            }
+        }
+        __syncwarp();
+        cluster_arrive();
+        cluster_wait();                                    // all partials have landed
+        phase_mark(6);
+        if (helper && ok) {
+            // step 3: own accumulators + the S-1 received slots -> epilogue for the owned columns
+            for (int cc0 = 0; cc0 < per && tb + cc0 < M; cc0 += 16) {
+                const int ncol = min(min(16, per - cc0), M - tb - cc0);
+                const int col = part * per + cc0;          // column inside the owned range
+                int v[16];
+                tmem_ld16(tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(crank * CWo + col), v);
+                for (int sl = 0; sl < S - 1; ++sl) {
+                    const uint32_t src = buf + (uint32_t)(sl * SLOT + (((col >> 2) * 128 + row) << 4));
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (4 * i < ncol) {
+                            const uint4 w = lds128(src + 2048 * i);
+                            v[4 * i] += (int)w.x, v[4 * i + 1] += (int)w.y, v[4 * i + 2] += (int)w.z, v[4 * i + 3] += (int)w.w;
+                        }
+                }
+#pragma unroll
+                for (int h = 0; h < 16; h += 8) {          // two halves: loads of a half before its stores
+                    float sc[8];
+                    __nv_bfloat16 res[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const bool live = h + j < ncol;
+                        sc[j] = (live && p.epilogue != EPI_RAW_I32) ? s_w[cc0 + h + j] : 1.f;
+                        res[j] = (live && n_ok && p.residual) ? p.residual[(long long)(tb + cc0 + h + j) * N + n]
+                                                              : __float2bfloat16_rn(0.f);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (h + j < ncol && n_ok) {
+                            const long long o = (long long)(tb + cc0 + h + j) * N + n;
+                            if (p.epilogue == EPI_RAW_I32) reinterpret_cast<int*>(p.out)[o] = v[h + j];
+                            else if (p.epilogue == EPI_F32_DIV) reinterpret_cast<float*>(p.out)[o] = __fdiv_rn(__int2float_rn(v[h + j]), sc[j]);
+                            else {
+                                __nv_bfloat16 r = fast ? __float2bfloat16_rn(__fmul_rn(__int2float_rn(v[h + j]), sc[j]))
+                                                       : scale_epilogue(v[h + j], sc[j], ws_el, p.epilogue);
+                                if (p.residual) r = __float2bfloat16_rn(__bfloat162float(res[j]) + __bfloat162float(r));
+                                reinterpret_cast<__nv_bfloat16*>(p.out)[o] = r;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (tid == kLgFirstEpi * 32) phase_mark_here(7);
     if (*abort_flag && tid == 0) atomicExch(p.status, ST_WAIT_TIMEOUT);
     tc_fence_before();
     __syncthreads();
+    phase_mark(8);
     if (warp == 1) tmem_dealloc(tmem_base, 2 * NT);
 }
 

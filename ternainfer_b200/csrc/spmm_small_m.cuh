@@ -61,8 +61,16 @@ __device__ __forceinline__ void phase_mark(int k) {
         if (cta < 4096) g_phase_log[cta * kPhaseSlots + k] = t;
     }
 }
+// the calling thread records (for kernels whose roles live in different warps)
+__device__ __forceinline__ void phase_mark_here(int k) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    if (cta < 4096) g_phase_log[cta * kPhaseSlots + k] = t;
+}
 #else
 __device__ __forceinline__ void phase_mark(int) {}
+__device__ __forceinline__ void phase_mark_here(int) {}
 #endif
 
 constexpr int kRedStride = 68;                     // ints per token row of the reduction buffer (conflict-free)

@@ -53,14 +53,16 @@ static int device_sm_count() {
 // TERNASPMM_CTAS_PER_SM_X10 (0 = automatic one-wave choice),
 // TERNASPMM_MAX_WARPS (cap on warps per CTA), TERNASPMM_PDL=0 to launch
 // without programmatic dependent launch, TERNASPMM_LARGE_MIN_M = smallest
-// token count sent to the tcgen05 kernel (default 33).
+// token count sent to the tcgen05 kernel (default 33), TERNASPMM_LARGE_SPLIT=0
+// to run that kernel without its cluster K split.
 struct Tuning {
-    int ctas_x10 = 0, max_warps = 0, pdl = 1, large_min_m = 33;
+    int ctas_x10 = 0, max_warps = 0, pdl = 1, large_min_m = 33, large_split = 1;
     Tuning() {
         if (const char* e = getenv("TERNASPMM_CTAS_PER_SM_X10")) ctas_x10 = atoi(e);
         if (const char* e = getenv("TERNASPMM_MAX_WARPS")) max_warps = atoi(e);
         if (const char* e = getenv("TERNASPMM_PDL")) pdl = atoi(e) != 0;
         if (const char* e = getenv("TERNASPMM_LARGE_MIN_M")) large_min_m = atoi(e) > 0 ? atoi(e) : large_min_m;
+        if (const char* e = getenv("TERNASPMM_LARGE_SPLIT")) large_split = atoi(e) != 0;
     }
 };
 static const Tuning& tuning() {
@@ -164,9 +166,10 @@ static bool encode_x_map(CUtensorMap* map, const void* x, int M, int K, int NT) 
 }
 
 template <int NT>
-static cudaError_t launch_large_m(const SpmmParams& p, cudaStream_t stream) {
+static cudaError_t launch_large_m(const SpmmParams& p_in, cudaStream_t stream) {
     using L = LargeMSmem<NT>;
     static bool attr_done[64] = {false};
+    static int max_clusters[64][4] = {};   // co-resident clusters of 2 / 4 / 8 CTAs (index log2), 0 = not asked yet
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
@@ -176,19 +179,50 @@ static cudaError_t launch_large_m(const SpmmParams& p, cudaStream_t stream) {
         if (e != cudaSuccess) return e;
         attr_done[dev] = true;
     }
+    SpmmParams p = p_in;
     CUtensorMap map;
     if (!encode_x_map(&map, p.x, p.M, p.K, NT)) return cudaErrorInvalidValue;
-    cudaLaunchConfig_t cfg = {};
     const long long tiles = (long long)((p.N + 127) / 128) * ((p.M + NT - 1) / NT);
-    cfg.gridDim = dim3((unsigned)std::min<long long>(tiles, device_sm_count()), 1, 1);   // persistent: one CTA per SM
+    const int sms = device_sm_count(), KS = (p.K + kLgKStep - 1) / kLgKStep;
+    cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(L::threads, 1, 1);
     cfg.dynamicSmemBytes = L::total;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = tuning().pdl ? 1 : 0;
+    cfg.numAttrs = tuning().pdl ? 2 : 1;
+    // K split over a cluster when the tiles alone would leave more than half of the SMs idle:
+    // the largest cluster of 2/4/8 CTAs that still fits the chip in one wave with >= 2 k-steps per CTA.
+    p.splits = 1;
+    if (tiles * 2 <= sms && tuning().large_split) {
+        for (int lg = 3; lg >= 1; --lg) {
+            const int S = 1 << lg;
+            if (tiles * S > sms || KS < 2 * S || NT / S < 16) continue;
+            if (max_clusters[dev][lg] == 0) {
+                cfg.gridDim = dim3((unsigned)(tiles * S), 1, 1);
+                attr[0].val.clusterDim.x = S;
+                int n = 0;
+                if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+                    cudaGetLastError();
+                    n = 0;
+                }
+                max_clusters[dev][lg] = n > 0 ? n : -1;
+            }
+            if (max_clusters[dev][lg] >= tiles) {
+                p.splits = S;
+                break;
+            }
+        }
+    }
+    attr[0].val.clusterDim.x = p.splits;
+    // persistent: one CTA per SM walks over the tiles (with a K split: one tile per cluster)
+    cfg.gridDim = dim3(p.splits > 1 ? (unsigned)(tiles * p.splits) : (unsigned)std::min<long long>(tiles, sms), 1, 1);
     return cudaLaunchKernelEx(&cfg, kern, p, map);
 }
 
@@ -245,10 +279,11 @@ static void run_spmm(int8_t* x, uint64_t* bitmap, int* tile_off, uint16_t* quart
     }
     cudaError_t e;
     // Kernel choice.  Up to 32 tokens: the small-batch kernel.  Above that the
-    // tcgen05 kernel, except for narrow weights at up to 128 tokens, where its
-    // 128-row tiles would occupy less than half of the SMs and the small-batch
-    // kernel run over blocks of 32 tokens is faster.
-    const bool narrow = M <= 128 && (N + 127) / 128 < device_sm_count() / 2;
+    // tcgen05 kernel (with its cluster K split when the 128-row tiles alone
+    // would occupy less than half of the SMs), except for small narrow weights
+    // at up to 64 tokens, where the small-batch kernel run over two blocks of
+    // 32 tokens is still a little faster (measured on the BitNet-2B shapes).
+    const bool narrow = M <= 64 && (N + 127) / 128 < device_sm_count() / 2 && (long long)N * K <= (32ll << 20);
     if (M >= tuning().large_min_m && !(narrow && tuning().large_min_m == 33)) {
         p.splits = 1;
         e = M <= 64 ? launch_large_m<64>(p, stream) : (M <= 128 ? launch_large_m<128>(p, stream) : launch_large_m<256>(p, stream));

@@ -302,3 +302,17 @@ def test_persistent_ctas_with_several_tiles_each(lib, M, N, K):
     got = call(lib, "bitlinear_TernaSpMM", xq, pk, sb, wb, 2)
     assert lib.ternaspmm_last_status() == 0
     assert (got == want).all()
+
+
+@pytest.mark.parametrize("M,N,K,ws_num", [(256, 1024, 2560, 1), (200, 2560, 2560, 1), (300, 2560, 6912, 1),
+                                          (130, 512, 4096, 2), (1000, 1152, 1024, 3), (512, 3840, 2560, 3)])
+def test_cluster_k_split_of_the_tensor_core_kernel(lib, M, N, K, ws_num):
+    """Few output tiles: the tcgen05 kernel runs as clusters of 8 / 4 / 2 CTAs per tile, each with a
+    slice of K, partial accumulators reduce-scattered through distributed shared memory.  Integer
+    addition is exact, so accumulators and bf16 outputs must not change by a bit."""
+    check(lib, M, N, K, ws_num)
+    w = o.make_ternary(N, K, 0.45, seed=M + N)
+    xq = np.random.default_rng(K).integers(-128, 128, size=(M, K), dtype=np.int8)
+    assert (accumulate(lib, xq, Packed(w)) == c_oracle.ternaspmm(xq, w, np.full(M, 0x3F80, np.uint16),
+                                                               np.full(4, 0x3F80, np.uint16), 1)[0]).all()
+    assert lib.ternaspmm_last_status() == 0
