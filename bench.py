@@ -109,6 +109,12 @@ class ClockSampler:
 # only as the thing to compare against, never on the GPU arm's path).
 # ----------------------------------------------------------------------------
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of spmm_small_m_kernel from one ncu capture of the
+# four layer shapes at full size (profiles/spmm_small_m_bitnet2b_sweep_M8.md: 1.985 + 1.339 + 7.011 + 3.566 MB),
+# averaged like the step's launches (each shape once per layer); token count -> bytes.
+NCU_DRAM_BYTES_PER_LAUNCH = {8: (1.985e6 + 1.339e6 + 7.011e6 + 3.566e6) / 4}
+
+
 def cpu_sample(tokens, seconds_budget, seed=1234):
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import ternaspmm_oracle as o
@@ -134,7 +140,7 @@ def cpu_sample(tokens, seconds_budget, seed=1234):
     t0 = time.perf_counter()
     one_pass()
     dt = time.perf_counter() - t0
-    reps = max(1, min(200, int(seconds_budget / max(dt, 1e-6))))
+    reps = max(1, min(2000, int(seconds_budget / max(dt, 1e-6))))
     return one_pass, alg, cores, reps, dt
 
 
@@ -142,7 +148,7 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    one_pass, alg, cores, reps, _ = cpu_sample(args.tokens, 2.0)
+    one_pass, alg, cores, reps, _ = cpu_sample(args.tokens, 4.0)
     for _ in range(args.warmup):
         one_pass()
     t0 = time.perf_counter()
@@ -291,24 +297,34 @@ def run_gpu_arm(args):
     d2h = sum(v.numel() * v.element_size() for v in out_host)
 
     # The calls go through the Python call site (TernaInfer_linear) once, under CUDA-graph capture,
-    # exactly as the reference's generate.py captures its forward; a step then is: copy this step's
-    # activations from pinned host memory, replay, copy every output back to pinned host memory.
+    # exactly as the reference's generate.py captures its forward.  The copies are part of the
+    # captured step: this step's activations come from pinned host memory on the main stream, and
+    # every output goes back to pinned host memory on a side stream that forks after its producer,
+    # so the device-to-host copies overlap the following linears.  A step is one replay.
     e2e_outs = []
     e2e_graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(device=device)
     with torch.cuda.stream(stream):
         with torch.cuda.graph(e2e_graph, stream=stream):
-            for it in work:
+            for K in xq_host:
+                xq_dev[K].copy_(xq_host[K], non_blocking=True)
+                s_dev[K].copy_(s_host[K], non_blocking=True)
+            for it, oh in zip(work, out_host):
                 K = it["K"]
-                e2e_outs.append(TernaInfer_linear(xq_dev[K], it["cv"], it["tg"], it["tm"], it["bm"], None, s_dev[K],
-                                                  it["ws"], it["ws_num"], it["N"]))
+                y = TernaInfer_linear(xq_dev[K], it["cv"], it["tg"], it["tm"], it["bm"], None, s_dev[K],
+                                      it["ws"], it["ws_num"], it["N"])
+                e2e_outs.append(y)
+                done = torch.cuda.Event()
+                done.record(stream)
+                side.wait_event(done)
+                with torch.cuda.stream(side):
+                    oh.copy_(y, non_blocking=True)
+            joined = torch.cuda.Event()
+            joined.record(side)
+            stream.wait_event(joined)
 
     def e2e_step():
-        for K in xq_host:
-            xq_dev[K].copy_(xq_host[K], non_blocking=True)
-            s_dev[K].copy_(s_host[K], non_blocking=True)
         e2e_graph.replay()
-        for y, oh in zip(e2e_outs, out_host):
-            oh.copy_(y, non_blocking=True)
 
     with torch.cuda.stream(stream):
         for _ in range(max(3, args.warmup)):
@@ -333,7 +349,7 @@ def run_gpu_arm(args):
         per_launch_us = ms_max * 1e3 / (args.steps * launches)
         achieved = (alg_step / launches) / (per_launch_us * 1e-6) / 1e9
         e2e_val = alg_step * world * args.steps / (e2e_ms * 1e-3) / 1e9
-        one_pass, cpu_alg, cores, reps, dt = cpu_sample(M, 3.0)
+        one_pass, cpu_alg, cores, reps, dt = cpu_sample(M, 10.0)
         t0 = time.perf_counter()
         for _ in range(reps):
             one_pass()
@@ -354,12 +370,13 @@ def run_gpu_arm(args):
                          "frac": achieved / peak, "peak_kind": "of " + peak_kind,
                          "frac_of_nominal_8000": achieved / 8000.0,
                          "kernel": "spmm_small_m_kernel", "avg_launch_us": per_launch_us,
-                         "algorithmic_bytes_per_launch": alg_step / launches, "traffic": None},
+                         "algorithmic_bytes_per_launch": alg_step / launches,
+                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(M)},
             "cpu_baseline": {"value": cpu_alg * reps / cpu_dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
                              "sample": f"{reps} passes over one layer (4 linears) at {M} tokens, dense int8 ternary "
                                        f"weights, {cpu_dt:.1f} s"},
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms / args.steps, "api": "ternainfer_b200.linear.TernaInfer_linear captured in a CUDA graph; H2D + replay + D2H per step"},
+                    "ms_per_step": e2e_ms / args.steps, "api": "ternainfer_b200.linear.TernaInfer_linear captured in a CUDA graph together with its H2D and (side-stream) D2H copies; one replay per step"},
             "gpu_launches": launches * args.steps,
             "clocks": clocks,
         }
