@@ -56,13 +56,17 @@ static int device_sm_count() {
 // token count sent to the tcgen05 kernel (default 33), TERNASPMM_LARGE_SPLIT=0
 // to run that kernel without its cluster K split.
 struct Tuning {
-    int ctas_x10 = 0, max_warps = 0, pdl = 1, large_min_m = 33, large_split = 1;
+    int ctas_x10 = 0, max_warps = 0, pdl = 1, large_min_m = 33, large_split = 1, cluster_cost_x10 = 0, fat = 1, force_s = 0, force_w = 0;
     Tuning() {
         if (const char* e = getenv("TERNASPMM_CTAS_PER_SM_X10")) ctas_x10 = atoi(e);
         if (const char* e = getenv("TERNASPMM_MAX_WARPS")) max_warps = atoi(e);
         if (const char* e = getenv("TERNASPMM_PDL")) pdl = atoi(e) != 0;
         if (const char* e = getenv("TERNASPMM_LARGE_MIN_M")) large_min_m = atoi(e) > 0 ? atoi(e) : large_min_m;
         if (const char* e = getenv("TERNASPMM_LARGE_SPLIT")) large_split = atoi(e) != 0;
+        if (const char* e = getenv("TERNASPMM_CLUSTER_COST_X10")) cluster_cost_x10 = atoi(e);
+        if (const char* e = getenv("TERNASPMM_FAT")) fat = atoi(e);
+        if (const char* e = getenv("TERNASPMM_FORCE_S")) force_s = atoi(e);
+        if (const char* e = getenv("TERNASPMM_FORCE_W")) force_w = atoi(e);
     }
 };
 static const Tuning& tuning() {
@@ -84,6 +88,7 @@ static LaunchShape choose_shape(int RT, int KT, int token_blocks, int max_warps,
     const long long rows = (long long)RT * token_blocks;
     const int max_w = tuning().max_warps > 0 && tuning().max_warps < max_warps ? tuning().max_warps : max_warps;
     const int max_s = KT > 1 ? (KT / 2 < 8 ? KT / 2 : 8) : 1;
+    if (tuning().force_s > 0 && tuning().force_w > 0) return {tuning().force_s, tuning().force_w};
     if (tuning().ctas_x10 > 0) {
         const long long target = (long long)tuning().ctas_x10 * sms / 10;
         int s = (int)((target + rows - 1) / rows);
@@ -91,6 +96,9 @@ static LaunchShape choose_shape(int RT, int KT, int token_blocks, int max_warps,
         const int nt = (KT + s - 1) / s;
         return {s, nt < 2 ? 2 : (nt > max_w ? max_w : nt)};
     }
+    // cost of a candidate in tenths of a tile time: tiles per warp, plus the cluster reduction when K is split
+    LaunchShape best = {0, 0};
+    long long best_cost = -1;
     for (int tpw = 1; tpw <= KT; ++tpw)
         for (int s = 1; s <= max_s; ++s) {
             const int nt = (KT + s - 1) / s;
@@ -99,21 +107,48 @@ static LaunchShape choose_shape(int RT, int KT, int token_blocks, int max_warps,
             if (w < 2) w = 2;
             int per_sm = warp_slots / w;
             per_sm = per_sm > 2 ? 2 : per_sm;
-            if (rows * s <= (long long)sms * per_sm) return {s, w};
+            if (per_sm < 1 || rows * s > (long long)sms * per_sm) continue;
+            const long long cost = 10ll * tpw + (s > 1 ? tuning().cluster_cost_x10 : 0);
+            if (best_cost < 0 || cost < best_cost) best = {s, w}, best_cost = cost;
         }
+    if (best_cost >= 0) return best;
     // more than one wave whatever we do: no K split, full CTAs
     return {1, KT < 2 ? 2 : (KT > max_w ? max_w : KT)};
 }
 
+// "Fat" shape: one CTA per SM with as many warps as the register file allows.  Measured on the
+// BitNet-2B layers (QKV at 8 tokens: 5.3 -> 3.4 us), a launch whose row tiles fit the SMs once is
+// fastest without any K split as long as a warp gets at most 2 (3 for 32-token blocks) tiles, and
+// otherwise with the smallest split that gets there while the clusters still fit the chip in one
+// wave; more CTAs than SMs (two thin CTAs per SM, each building its own tables) are slower.
+// Returns splits = 0 when the thin shape should be used instead.
+static LaunchShape choose_fat(int RT, int KT, int token_blocks, int max_warps, int mt) {
+    const int sms = device_sm_count();
+    const long long rows = (long long)RT * token_blocks;
+    if (!tuning().fat || rows > sms) return {0, 0};
+    const int max_s = KT > 1 ? (KT / 2 < 8 ? KT / 2 : 8) : 1;
+    const int limit = mt >= 4 ? 3 : 2;
+    int pick = 0;
+    for (int s = 1; s <= max_s && rows * s <= sms; ++s) {
+        const int nt = (KT + s - 1) / s;
+        pick = s;                                            // the largest feasible split if none reaches the limit
+        if ((nt + max_warps - 1) / max_warps <= limit) break;
+    }
+    if (pick == 0 || (mt == 1 && pick > 1)) return {0, 0};   // at 8 tokens a split runs better as thin CTAs
+    const int nt = (KT + pick - 1) / pick;
+    return {pick, nt < 2 ? 2 : (nt > max_warps ? max_warps : nt)};
+}
+
 template <int MT, int MAXW, int MINB>
-static cudaError_t launch_small_m(SpmmParams& p, int token_blocks, int warp_slots, cudaStream_t stream) {
+static cudaError_t launch_small_m(SpmmParams& p, int token_blocks, int warp_slots, cudaStream_t stream,
+                                  LaunchShape preset = {0, 0}) {
     using L = SmallMSmem<MT>;
     static bool attr_done[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
     auto kern = spmm_small_m_kernel<MT, MAXW, MINB>;
-    const LaunchShape shape = choose_shape(p.N / 64, p.K / 64, token_blocks, MAXW, warp_slots);
+    const LaunchShape shape = preset.splits > 0 ? preset : choose_shape(p.N / 64, p.K / 64, token_blocks, MAXW, warp_slots);
     p.splits = shape.splits;
     const int warps = shape.warps;
     if (!attr_done[dev]) {
@@ -287,12 +322,20 @@ static void run_spmm(int8_t* x, uint64_t* bitmap, int* tile_off, uint16_t* quart
     if (M >= tuning().large_min_m && !(narrow && tuning().large_min_m == 33)) {
         p.splits = 1;
         e = M <= 64 ? launch_large_m<64>(p, stream) : (M <= 128 ? launch_large_m<128>(p, stream) : launch_large_m<256>(p, stream));
-    } else if (M <= 8) {
-        e = launch_small_m<1, 14, 2>(p, 1, 28, stream);
-    } else if (M <= 16) {
-        e = launch_small_m<2, 10, 2>(p, 1, 20, stream);
     } else {
-        e = launch_small_m<4, 8, 2>(p, (M + 31) / 32, 16, stream);
+        // thin: up to two CTAs per SM; fat: one CTA per SM with twice the warps (see choose_fat)
+        const int RT = N / 64, KT = K / 64;
+        if (M <= 8) {
+            const LaunchShape fat = choose_fat(RT, KT, 1, 28, 1);
+            e = fat.splits ? launch_small_m<1, 28, 1>(p, 1, 28, stream, fat) : launch_small_m<1, 14, 2>(p, 1, 28, stream);
+        } else if (M <= 16) {
+            const LaunchShape fat = choose_fat(RT, KT, 1, 20, 2);
+            e = fat.splits ? launch_small_m<2, 20, 1>(p, 1, 20, stream, fat) : launch_small_m<2, 10, 2>(p, 1, 20, stream);
+        } else {
+            const int tb = (M + 31) / 32;
+            const LaunchShape fat = choose_fat(RT, KT, tb, 16, 4);
+            e = fat.splits ? launch_small_m<4, 16, 1>(p, tb, 16, stream, fat) : launch_small_m<4, 8, 2>(p, tb, 16, stream);
+        }
     }
     if (e != cudaSuccess) {
         fprintf(stderr, "ternaspmm: launch failed: %s\n", cudaGetErrorString(e));
