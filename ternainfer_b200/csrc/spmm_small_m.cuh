@@ -39,6 +39,7 @@ struct SpmmParams {
     const __nv_bfloat16* ws;     // [4]
     const __nv_bfloat16* residual;  // optional bf16 [M][N] added to the rounded result (residual stream), or null
     int ws_num, M, N, K, epilogue, splits;
+    int stage_second;            // small-batch kernel: every warp has a 4 KB shared-memory slot for its second tile
     int seg_b[3];   // first output column of scale segments 1, 2, 3 (INT_MAX when absent)
     int seg_gran;   // 1, or the reference's granularity: 8 (decode form) / 128 (prefill form)
     int* status;
@@ -267,6 +268,23 @@ __device__ __forceinline__ void decode_tile(const TileHead& h, const TileSigns& 
     }
 }
 
+// Decode one tile into a warp's 4 KB shared-memory slot: word r -> two 16-byte stores per lane
+// ([2r + half][lane], 512 contiguous bytes per store instruction).
+__device__ __forceinline__ void decode_tile_to_smem(const TileHead& h, const TileSigns& sg, uint32_t lut_lo, uint32_t lut_hi,
+                                                    uint32_t slot_lane) {
+    const uint32_t w[4] = {h.bw.x, h.bw.y, h.bw.z, h.bw.w};
+    int pos = sg.pos;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int c = __popc(w[r]);
+        uint32_t a[8];
+        decode_word2(w[r], __funnelshift_r(sg.lo[r], sg.hi[r], (uint32_t)pos), c, lut_lo, lut_hi, a);
+        sts128(slot_lane + (2 * r) * 512, make_uint4(a[0], a[1], a[2], a[3]));
+        sts128(slot_lane + (2 * r + 1) * 512, make_uint4(a[4], a[5], a[6], a[7]));
+        pos += c;
+    }
+}
+
 template <int MT>
 __device__ __forceinline__ void load_x_frags(uint4 (&bx)[MT], const int8_t* x, int K, int m0, int mrows, int ktile,
                                              int g, int q) {
@@ -340,6 +358,16 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const Spm
     if (have_first) decode_tile(h_cur, s_cur, lut_lo, lut_hi, pre);
     TileSigns s_nxt = load_signs(p, h_nxt, kt + nwarps < kt1, lane);
     TileHead h_far = load_head(p, tile0 + kt + 2 * nwarps, kt + 2 * nwarps < kt1, lane);
+    // ---- and, where the launch gives every warp a shared-memory slot (one fat CTA per SM), the
+    // second tile too: after the wait only the activation loads and the MMAs are left for it
+    const bool staged = p.stage_second && kt + nwarps < kt1;
+    const uint32_t slot_lane = lut_base + kLut2Bytes + (uint32_t)L::rest + (uint32_t)(warp * 4096 + lane * 16);
+    if (staged) {
+        decode_tile_to_smem(h_nxt, s_nxt, lut_lo, lut_hi, slot_lane);
+        h_nxt = h_far;
+        s_nxt = load_signs(p, h_nxt, kt + 2 * nwarps < kt1, lane);
+        h_far = load_head(p, tile0 + kt + 3 * nwarps, kt + 3 * nwarps < kt1, lane);
+    }
     phase_mark(3);
 
     // ---- activations, scales and the output may belong to the previous kernel
@@ -358,6 +386,21 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const Spm
                 mma_s8_16x8x32(acc[r][mt], pre[r][0], pre[r][1], pre[r][2], pre[r][3], bx[mt].x, bx[mt].y);
                 mma_s8_16x8x32(acc[r][mt], pre[r][4], pre[r][5], pre[r][6], pre[r][7], bx[mt].z, bx[mt].w);
             }
+    }
+
+    if (staged) {
+        kt += nwarps;
+        uint4 bx[MT];
+        load_x_frags<MT>(bx, p.x, p.K, m0, mrows, kt, g, q);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const uint4 lo = lds128(slot_lane + (2 * r) * 512), hi = lds128(slot_lane + (2 * r + 1) * 512);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                mma_s8_16x8x32(acc[r][mt], lo.x, lo.y, lo.z, lo.w, bx[mt].x, bx[mt].y);
+                mma_s8_16x8x32(acc[r][mt], hi.x, hi.y, hi.z, hi.w, bx[mt].z, bx[mt].w);
+            }
+        }
     }
 
     // ---- remaining tiles of this warp: streamed through the register pipeline

@@ -56,7 +56,7 @@ static int device_sm_count() {
 // token count sent to the tcgen05 kernel (default 33), TERNASPMM_LARGE_SPLIT=0
 // to run that kernel without its cluster K split.
 struct Tuning {
-    int ctas_x10 = 0, max_warps = 0, pdl = 1, large_min_m = 33, large_split = 1, cluster_cost_x10 = 0, fat = 1, force_s = 0, force_w = 0;
+    int ctas_x10 = 0, max_warps = 0, pdl = 1, large_min_m = 33, large_split = 1, cluster_cost_x10 = 0, fat = 1, force_s = 0, force_w = 0, stage = 1;
     Tuning() {
         if (const char* e = getenv("TERNASPMM_CTAS_PER_SM_X10")) ctas_x10 = atoi(e);
         if (const char* e = getenv("TERNASPMM_MAX_WARPS")) max_warps = atoi(e);
@@ -65,6 +65,7 @@ struct Tuning {
         if (const char* e = getenv("TERNASPMM_LARGE_SPLIT")) large_split = atoi(e) != 0;
         if (const char* e = getenv("TERNASPMM_CLUSTER_COST_X10")) cluster_cost_x10 = atoi(e);
         if (const char* e = getenv("TERNASPMM_FAT")) fat = atoi(e);
+        if (const char* e = getenv("TERNASPMM_STAGE")) stage = atoi(e) != 0;
         if (const char* e = getenv("TERNASPMM_FORCE_S")) force_s = atoi(e);
         if (const char* e = getenv("TERNASPMM_FORCE_W")) force_w = atoi(e);
     }
@@ -151,8 +152,15 @@ static cudaError_t launch_small_m(SpmmParams& p, int token_blocks, int warp_slot
     const LaunchShape shape = preset.splits > 0 ? preset : choose_shape(p.N / 64, p.K / 64, token_blocks, MAXW, warp_slots);
     p.splits = shape.splits;
     const int warps = shape.warps;
+    // one CTA per SM (MINB == 1) leaves room for a 4 KB slot per warp: second tiles are decoded before the wait
+    // (only the warps that have a second tile need one: the first nt - warps of them)
+    const int nt = (p.K / 64 + shape.splits - 1) / shape.splits;
+    const int slots = (MINB == 1 && tuning().stage) ? std::max(0, std::min(warps, nt - warps)) : 0;
+    p.stage_second = slots > 0 ? 1 : 0;
+    const int smem_bytes = L::total + slots * 4096;
     if (!attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             L::total + (MINB == 1 ? MAXW * 4096 : 0));
         if (e != cudaSuccess) return e;
         attr_done[dev] = true;
     }
@@ -160,7 +168,7 @@ static cudaError_t launch_small_m(SpmmParams& p, int token_blocks, int warp_slot
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.splits, RT, token_blocks);
     cfg.blockDim = dim3(warps * 32, 1, 1);
-    cfg.dynamicSmemBytes = L::total;
+    cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
