@@ -19,7 +19,7 @@
 
 namespace tsp {
 
-constexpr int kActThreads = 256;
+constexpr int kActMaxThreads = 1024;   // one 8-element vector per thread up to K = 8192; longer rows loop
 
 __device__ __forceinline__ float bf16_round_f(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
@@ -34,7 +34,7 @@ __device__ __forceinline__ float block_reduce(float v, float* scratch, bool is_m
     if (lane == 0) scratch[warp] = v;
     __syncthreads();
     float r = scratch[0];
-    for (int i = 1; i < kActThreads / 32; ++i) r = is_max ? fmaxf(r, scratch[i]) : r + scratch[i];
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) r = is_max ? fmaxf(r, scratch[i]) : r + scratch[i];
     return r;
 }
 
@@ -46,14 +46,14 @@ enum ActMode : int { ACT_RMSNORM = 0, ACT_SCALE_SUMSQ = 1, ACT_PLAIN = 2 };
 // x: [M][ld] bf16 (GATED: the row holds [x1 (K) | x3 (K)], ld = 2K), w: [K] bf16 norm weight,
 // q: [M][K] int8, s_out: [M] bf16, ss_out: [M] fp32 (MODE 1).  Dynamic shared memory: K bf16.
 template <bool GATED, int MODE>
-__global__ void __launch_bounds__(kActThreads) norm_quant_kernel(const __nv_bfloat16* __restrict__ x,
+__global__ void __launch_bounds__(kActMaxThreads) norm_quant_kernel(const __nv_bfloat16* __restrict__ x,
                                                                   const __nv_bfloat16* __restrict__ w, float eps,
                                                                   int K, int8_t* __restrict__ q,
                                                                   __nv_bfloat16* __restrict__ s_out,
                                                                   float* __restrict__ ss_out) {
     extern __shared__ __align__(16) uint8_t act_smem[];
     __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(act_smem);
-    __shared__ float scratch[kActThreads / 32];
+    __shared__ float scratch[kActMaxThreads / 32];
     griddep_launch_dependents();
     griddep_wait();   // the activations come from the previous kernel
     const int t = blockIdx.x, tid = threadIdx.x;
@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(kActThreads) norm_quant_kernel(const __nv_bflo
 
     // pass 1: stage the row (after the gate, if any) and its sum of squares
     float ss = 0.f;
-    for (int k0 = tid * 8; k0 < K; k0 += kActThreads * 8) {
+    for (int k0 = tid * 8; k0 < K; k0 += blockDim.x * 8) {
         const uint4 a = *reinterpret_cast<const uint4*>(xr + k0);
         const __nv_bfloat16* av = reinterpret_cast<const __nv_bfloat16*>(&a);
         __align__(16) __nv_bfloat16 v[8];
@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(kActThreads) norm_quant_kernel(const __nv_bflo
 
     // pass 2: normalise, apply the weight, round to bf16, absmax
     float amax = 0.f;
-    for (int k0 = tid * 8; k0 < K; k0 += kActThreads * 8) {
+    for (int k0 = tid * 8; k0 < K; k0 += blockDim.x * 8) {
         uint4 a = *reinterpret_cast<const uint4*>(row + k0);
         __nv_bfloat16* av = reinterpret_cast<__nv_bfloat16*>(&a);
         if (MODE != ACT_PLAIN) {
@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(kActThreads) norm_quant_kernel(const __nv_bflo
     if (tid == 0) s_out[t] = __float2bfloat16_rn(s);
 
     // pass 3: quantise
-    for (int k0 = tid * 16; k0 < K; k0 += kActThreads * 16) {
+    for (int k0 = tid * 16; k0 < K; k0 += blockDim.x * 16) {
         __align__(16) int8_t o[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {

@@ -461,7 +461,7 @@ static void run_norm_quant(bool gated, int mode, __nv_bfloat16* x, __nv_bfloat16
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(M, 1, 1);
-    cfg.blockDim = dim3(kActThreads, 1, 1);
+    cfg.blockDim = dim3(std::min(kActMaxThreads, std::max(64, (K / 8 + 31) / 32 * 32)), 1, 1);   // one vector per thread
     cfg.dynamicSmemBytes = (size_t)K * 2;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
