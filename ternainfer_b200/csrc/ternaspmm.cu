@@ -334,7 +334,8 @@ static void run_spmm(int8_t* x, uint64_t* bitmap, int* tile_off, uint16_t* quart
         // thin: up to two CTAs per SM; fat: one CTA per SM with twice the warps (see choose_fat)
         const int RT = N / 64, KT = K / 64;
         if (M <= 8) {
-            const LaunchShape fat = choose_fat(RT, KT, 1, 28, 1);
+            LaunchShape fat = choose_fat(RT, KT, 1, 28, 1);
+            if (tuning().force_s > 0 && tuning().force_w > 14) fat = {tuning().force_s, tuning().force_w};   // tuning runs
             e = fat.splits ? launch_small_m<1, 28, 1>(p, 1, 28, stream, fat) : launch_small_m<1, 14, 2>(p, 1, 28, stream);
         } else if (M <= 16) {
             const LaunchShape fat = choose_fat(RT, KT, 1, 20, 2);
