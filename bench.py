@@ -110,9 +110,9 @@ class ClockSampler:
 # ----------------------------------------------------------------------------
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of spmm_small_m_kernel from one ncu capture of the
-# four layer shapes at full size (profiles/spmm_small_m_bitnet2b_sweep_M8.md: 1.985 + 1.339 + 7.011 + 3.566 MB),
+# four layer shapes at full size (profiles/spmm_small_m_bitnet2b_sweep_M8.md: 1.991 + 1.346 + 7.018 + 3.573 MB),
 # averaged like the step's launches (each shape once per layer); token count -> bytes.
-NCU_DRAM_BYTES_PER_LAUNCH = {8: (1.985e6 + 1.339e6 + 7.011e6 + 3.566e6) / 4}
+NCU_DRAM_BYTES_PER_LAUNCH = {8: (1.991e6 + 1.346e6 + 7.018e6 + 3.573e6) / 4}
 
 
 def cpu_sample(tokens, seconds_budget, seed=1234):
@@ -527,6 +527,67 @@ def run_tp_arm(args):
 # of seeded random ids, greedy generation; value = decode tokens per second.
 # ----------------------------------------------------------------------------
 
+def cpu_decode_sample(bsz, layers, seconds_budget=10.0, seed=1234):
+    """PyTorch-CPU model path of one decode step, timed on the host cores: one decoder layer of the
+    BitNet-2B architecture as the reference's dense comparator computes it (quant_input, F.linear on
+    the de-quantised ternary weight, division by the scale; RMSNorm and sub-layer norms, RoPE,
+    attention over a 640-token bf16 cache, relu^2 gate) plus the tied output head, all float32
+    torch CPU ops.  A step costs `layers` x the layer time + the head time; returns tokens/s."""
+    import torch
+    import torch.nn.functional as F
+    torch.manual_seed(seed)
+    dim, H, Hkv, D, ffn, vocab, L = 2560, 20, 5, 128, 6912, 128256, 640
+    cores = torch.get_num_threads()
+
+    def tern(n, k):
+        r = torch.rand(n, k)
+        return torch.where(r < P_ZERO, torch.zeros(()), torch.where(torch.rand(n, k) < 0.5, -torch.ones(()), torch.ones(())))
+
+    wqkv, wo, w13, w2 = tern((H + 2 * Hkv) * D, dim), tern(dim, dim), tern(2 * ffn, dim), tern(dim, ffn)
+    head = torch.randn(vocab, dim) * 0.02
+    ck, cv = torch.randn(bsz, Hkv, L, D), torch.randn(bsz, Hkv, L, D)
+    g = [torch.ones(dim), torch.ones(dim), torch.ones(dim), torch.ones(ffn)]
+
+    def norm(x, w):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * w
+
+    def lin(x, w):
+        s = 127 / x.abs().max(-1, keepdim=True).values.clamp(min=1e-5)
+        return F.linear((x * s).round().clamp(-128, 127), w) / s * 0.02
+
+    def layer(x):
+        qkv = lin(norm(x, g[0]), wqkv)
+        q = qkv[:, : H * D].view(bsz, 1, H, D).transpose(1, 2)
+        k = qkv[:, H * D: (H + Hkv) * D].view(bsz, Hkv, 1, D)
+        v = qkv[:, (H + Hkv) * D:].view(bsz, Hkv, 1, D)
+        ck[:, :, L - 1: L], cv[:, :, L - 1: L] = k, v
+        o = F.scaled_dot_product_attention(q, ck.repeat_interleave(H // Hkv, 1), cv.repeat_interleave(H // Hkv, 1))
+        h = x + lin(norm(o.transpose(1, 2).reshape(bsz, H * D), g[1]), wo)
+        x13 = lin(norm(h, g[2]), w13)
+        inner = torch.relu(x13[:, :ffn]) ** 2 * x13[:, ffn:]
+        return h + lin(norm(inner, g[3]), w2)
+
+    x = torch.randn(bsz, dim)
+    with torch.inference_mode():
+        layer(x), F.linear(x, head)
+        t0 = time.perf_counter()
+        layer(x)
+        one = time.perf_counter() - t0
+        reps = max(2, min(200, int(0.7 * seconds_budget / max(one, 1e-6))))
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            x = layer(x)
+        t_layer = (time.perf_counter() - t0) / reps
+        hreps = max(2, min(50, int(0.3 * seconds_budget / max(one * 4, 1e-6))))
+        t0 = time.perf_counter()
+        for _ in range(hreps):
+            F.linear(x, head)
+        t_head = (time.perf_counter() - t0) / hreps
+    step = layers * t_layer + t_head
+    return bsz / step, cores, f"{reps} passes of one decoder layer and {hreps} of the output head at batch {bsz}, " \
+                               f"float32 torch CPU ops; step = {layers} x layer + head"
+
+
 def run_decode_arm(args):
     import torch
     from ternainfer_b200.generate import FastGen, GenArgs, build_random_model
@@ -556,6 +617,8 @@ def run_decode_arm(args):
                        "generate": 128, "fused_glue": not args.unfused, "seed": args.seed,
                        "prefill_tokens_per_s": best["prefill_tokens_per_s"]},
             "clocks": clocks}
+    cpu_tps, cores, sample = cpu_decode_sample(bsz, args.layers)
+    line["cpu_baseline"] = {"value": cpu_tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
     print(json.dumps(line), flush=True)
 
 
