@@ -62,11 +62,11 @@ struct LargeMSmem {
     static constexpr int tmem_slot = 136;
     static constexpr int abort_flag = 140;
     static constexpr int scl = 256;                        // float s[NT / 2] per epilogue warp
-    static constexpr int lut1 = scl + kLgEpiWarps * (NT / 2) * 4;   // the 256 table entries, one copy
-    static constexpr int a = (lut1 + 1024 + 1023) / 1024 * 1024;
+    static constexpr int a = (scl + kLgEpiWarps * (NT / 2) * 4 + 1023) / 1024 * 1024;
     static constexpr int b = a + stages * kLgAStage;
     static constexpr int rest = b + stages * NT * kLgKStep;
-    static constexpr int total = 2 * kLutBytes + rest;     // table aligned to 32 KB, the rest behind it
+    static constexpr int tables = NT <= 64 ? 2 : 1;        // the two-table decode where shared memory allows it
+    static constexpr int total = (tables + 1) * kLutBytes + rest;   // tables aligned to 32 KB, the rest behind them
 };
 
 // ---- tcgen05 wrappers ------------------------------------------------------
@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(LargeMSmem<NT>::threads, 1)
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t dyn = smem_u32(smem);
     const uint32_t lut_base = (dyn + (uint32_t)kLutBytes - 1u) & ~((uint32_t)kLutBytes - 1u);
-    const uint32_t sbase = lut_base + kLutBytes;  // 32 KB aligned, so the stage buffers are 1024-byte aligned
+    const uint32_t sbase = lut_base + L::tables * kLutBytes;  // 32 KB aligned, so the stage buffers are 1024-byte aligned
     uint8_t* rest = smem + (sbase - dyn);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(rest + L::abort_flag);
     float* s_s = reinterpret_cast<float*>(rest + L::scl);
@@ -182,12 +182,11 @@ __global__ void __launch_bounds__(LargeMSmem<NT>::threads, 1)
         *abort_flag = 0;
         mbar_fence_init();
     }
-    for (int e = tid; e < 256; e += L::threads) reinterpret_cast<uint32_t*>(rest + L::lut1)[e] = lut_entry(e);
+    // (the one-copy tables are staged in the first pipeline stage, which is idle until the loop starts)
+    uint32_t* lut1 = reinterpret_cast<uint32_t*>(rest + L::a);
+    for (int e = tid; e < 256 * L::tables; e += L::threads) lut1[e] = e < 256 ? lut_entry(e) : lut_entry_upper(e - 256);
     __syncthreads();
-    for (int i = tid; i < 256 * 8; i += L::threads) {
-        const uint32_t v = reinterpret_cast<const uint32_t*>(rest + L::lut1)[i >> 3];
-        sts128(lut_base + i * 16, make_uint4(v, v, v, v));
-    }
+    for (int i = tid; i < 256 * 8 * L::tables; i += L::threads) sts128(lut_base + i * 16, make_uint4(lut1[i >> 3], lut1[i >> 3], lut1[i >> 3], lut1[i >> 3]));
     if (warp == 1) tmem_alloc(sbase + L::tmem_slot, 2 * NT);
     tc_fence_before();
     __syncthreads();
@@ -293,8 +292,10 @@ __global__ void __launch_bounds__(LargeMSmem<NT>::threads, 1)
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
                     uint32_t a[8];
-                    decode_word(w[r], __funnelshift_r(s_cur.lo[r], s_cur.hi[r], (uint32_t)pos), lut_lane, a);
-                    pos += __popc(w[r]);
+                    const int c = __popc(w[r]);
+                    if (L::tables == 2) decode_word2(w[r], __funnelshift_r(s_cur.lo[r], s_cur.hi[r], (uint32_t)pos), c, lut_lane, 0u, a);
+                    else decode_word(w[r], __funnelshift_r(s_cur.lo[r], s_cur.hi[r], (uint32_t)pos), lut_lane, a);
+                    pos += c;
 #pragma unroll
                     for (int h = 0; h < 2; ++h)
                         sts128(a_lane + (uint32_t)((16 * r + 8 * h) * 128), make_uint4(a[h], a[2 + h], a[4 + h], a[6 + h]));
