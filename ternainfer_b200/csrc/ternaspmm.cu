@@ -49,14 +49,19 @@ static int device_sm_count() {
     return sms[dev];
 }
 
-// Launch-shape knobs, read once from the environment (for tuning runs):
-// TERNASPMM_CTAS_PER_SM_X10 (0 = automatic one-wave choice),
-// TERNASPMM_MAX_WARPS (cap on warps per CTA), TERNASPMM_PDL=0 to launch
-// without programmatic dependent launch, TERNASPMM_LARGE_MIN_M = smallest
-// token count sent to the tcgen05 kernel (default 33), TERNASPMM_LARGE_SPLIT=0
-// to run that kernel without its cluster K split.
+// Launch-shape knobs, read once from the environment (for tuning runs; the defaults are the product):
+//   TERNASPMM_PDL=0              launch without programmatic dependent launch
+//   TERNASPMM_FAT=0              small-batch kernel: never use the one-CTA-per-SM shape
+//   TERNASPMM_STAGE=0            small-batch kernel: no shared-memory slot for a warp's second tile
+//   TERNASPMM_FORCE_S / _FORCE_W small-batch kernel: this K split and this many warps per CTA
+//   TERNASPMM_CTAS_PER_SM_X10    small-batch kernel, thin shape: about that many CTAs per SM (x10)
+//   TERNASPMM_MAX_WARPS          small-batch kernel, thin shape: cap on warps per CTA
+//   TERNASPMM_CLUSTER_COST_X10   small-batch kernel, thin shape: price of a K split in tenths of a tile time
+//   TERNASPMM_LARGE_MIN_M        smallest token count sent to the tcgen05 kernel (default 33)
+//   TERNASPMM_LARGE_SPLIT=0      tcgen05 kernel without its cluster K split
 struct Tuning {
-    int ctas_x10 = 0, max_warps = 0, pdl = 1, large_min_m = 33, large_split = 1, cluster_cost_x10 = 0, fat = 1, force_s = 0, force_w = 0, stage = 1;
+    int ctas_x10 = 0, max_warps = 0, pdl = 1, large_min_m = 33, large_split = 1, cluster_cost_x10 = 0, fat = 1,
+        force_s = 0, force_w = 0, stage = 1;
     Tuning() {
         if (const char* e = getenv("TERNASPMM_CTAS_PER_SM_X10")) ctas_x10 = atoi(e);
         if (const char* e = getenv("TERNASPMM_MAX_WARPS")) max_warps = atoi(e);
