@@ -349,11 +349,16 @@ def run_gpu_arm(args):
         per_launch_us = ms_max * 1e3 / (args.steps * launches)
         achieved = (alg_step / launches) / (per_launch_us * 1e-6) / 1e9
         e2e_val = alg_step * world * args.steps / (e2e_ms * 1e-3) / 1e9
-        one_pass, cpu_alg, cores, reps, dt = cpu_sample(M, 10.0)
-        t0 = time.perf_counter()
-        for _ in range(reps):
-            one_pass()
-        cpu_dt = time.perf_counter() - t0
+        cpu_baseline = None            # timed at N = 1 only (rank 0's host cores)
+        if world == 1:
+            one_pass, cpu_alg, cores, reps, dt = cpu_sample(M, 10.0)
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                one_pass()
+            cpu_dt = time.perf_counter() - t0
+            cpu_baseline = {"value": cpu_alg * reps / cpu_dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+                            "sample": f"{reps} passes over one layer (4 linears) at {M} tokens, dense int8 ternary "
+                                      f"weights, {cpu_dt:.1f} s"}
         line = {
             "metric": "ternaspmm_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_max / args.steps,
@@ -372,9 +377,7 @@ def run_gpu_arm(args):
                          "kernel": "spmm_small_m_kernel", "avg_launch_us": per_launch_us,
                          "algorithmic_bytes_per_launch": alg_step / launches,
                          "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(M)},
-            "cpu_baseline": {"value": cpu_alg * reps / cpu_dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
-                             "sample": f"{reps} passes over one layer (4 linears) at {M} tokens, dense int8 ternary "
-                                       f"weights, {cpu_dt:.1f} s"},
+            "cpu_baseline": cpu_baseline,
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / args.steps, "api": "ternainfer_b200.linear.TernaInfer_linear captured in a CUDA graph together with its H2D and (side-stream) D2H copies; one replay per step"},
             "gpu_launches": launches * args.steps,
