@@ -40,6 +40,7 @@ struct SpmmParams {
     const __nv_bfloat16* residual;  // optional bf16 [M][N] added to the rounded result (residual stream), or null
     int ws_num, M, N, K, epilogue, splits;
     int stage_second;            // small-batch kernel: every warp has a 4 KB shared-memory slot for its second tile
+    int rpc;                     // small-batch kernel: row tiles per CTA (1 or 2), each with blockDim/32/rpc warps
     int seg_b[3];   // first output column of scale segments 1, 2, 3 (INT_MAX when absent)
     int seg_gran;   // 1, or the reference's granularity: 8 (decode form) / 128 (prefill form)
     int* status;
@@ -80,11 +81,11 @@ constexpr int kRedStride = 68;                     // ints per token row of the 
 // shared window (the entry index is OR-ed into the address), which the
 // dynamic segment's base does not guarantee; the small buffers ("rest") go
 // into the gap in front of the tables when it is large enough, else behind.
-template <int MT>
+template <int MT, int RPC = 1>   // RPC: row tiles a CTA may cover (2 for the one-CTA-per-SM variants)
 struct SmallMSmem {
     static constexpr int lut1 = 0;                                // the 2 x 256 entries, one copy
-    static constexpr int red = lut1 + 2048;                       // int32 [MT*8][kRedStride]
-    static constexpr int scl = red + MT * 8 * kRedStride * 4;     // float s[MT*8], ws[4]
+    static constexpr int red = lut1 + 2048;                       // int32 [RPC row tiles][MT*8][kRedStride]
+    static constexpr int scl = red + RPC * MT * 8 * kRedStride * 4;   // float s[MT*8], ws[4]
     static constexpr int rest = (scl + (MT * 8 + 4) * 4 + 127) / 128 * 128;
     static constexpr int total = kLut2Bytes + kLutBytes + rest;   // worst case of the run-time placement
 };
@@ -298,7 +299,7 @@ __device__ __forceinline__ void load_x_frags(uint4 (&bx)[MT], const int8_t* x, i
 
 template <int MT, int MAXW, int MINB>
 __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const SpmmParams p) {
-    using L = SmallMSmem<MT>;
+    using L = SmallMSmem<MT, MINB == 1 ? 2 : 1>;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t dyn = (smem_u32(smem) + 127u) & ~127u;
     const uint32_t lut_base = (dyn + (uint32_t)kLutBytes - 1u) & ~((uint32_t)kLutBytes - 1u);
@@ -307,14 +308,18 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const Spm
     int* red = reinterpret_cast<int*>(rest + L::red);
     float* scl_s = reinterpret_cast<float*>(rest + L::scl);
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = (blockDim.x >> 5) / p.rpc;
     const int g = lane >> 2, q = lane & 3;
     const int rank = blockIdx.x, S = p.splits;
-    const int rt = blockIdx.y;
+    // Row tiles of this CTA: one, or two with half of the warps each (a fat CTA that covers 128 rows,
+    // for weights with more row tiles than SMs).  `nwarps` below = the warps that share a row tile.
+    const int rpc = p.rpc, sub = rpc == 2 ? warp / ((blockDim.x >> 5) >> 1) : 0;
+    const int rt = blockIdx.y * rpc + sub;
+    const bool rt_ok = rt * 64 < p.N;
     const int m0 = blockIdx.z * (MT * 8);
     const int mrows = min(p.M - m0, MT * 8);
     const int KT = p.K >> 6;
-    const int kt0 = (int)(((long long)KT * rank) / S), kt1 = (int)(((long long)KT * (rank + 1)) / S);
+    const int kt0 = (int)(((long long)KT * rank) / S), kt1 = rt_ok ? (int)(((long long)KT * (rank + 1)) / S) : kt0;
     const long long tile0 = (long long)rt * KT;
 
     phase_mark(0);
@@ -325,13 +330,14 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const Spm
     // ---- prologue: everything up to the dependency wait touches only
     // immutable weight data, so it may overlap the previous kernel.
     // First loads of this warp's pipeline (tiles kt0+warp, +nwarps, ...):
-    int kt = kt0 + warp;
+    int kt = kt0 + (warp - sub * nwarps);
+    int* red_w = red + sub * (MT * 8 * kRedStride);   // this row tile's reduction buffer
     TileHead h_cur = load_head(p, tile0 + kt, kt < kt1, lane);
     TileHead h_nxt = load_head(p, tile0 + kt + nwarps, kt + nwarps < kt1, lane);
     // lookup tables: the 2 x 256 entries once, then 32 copies (lane l reads bank l)
     for (int e = tid; e < 512; e += blockDim.x)
         reinterpret_cast<uint32_t*>(rest + L::lut1)[e] = e < 256 ? lut_entry(e) : lut_entry_upper(e - 256);
-    for (int i = tid; i < MT * 8 * kRedStride; i += blockDim.x) red[i] = 0;
+    for (int i = tid; i < rpc * MT * 8 * kRedStride; i += blockDim.x) red[i] = 0;
     __syncthreads();
     for (int i = tid; i < 512 * 8; i += blockDim.x) {
         const uint32_t v = reinterpret_cast<const uint32_t*>(rest + L::lut1)[i >> 3];
@@ -430,7 +436,7 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const Spm
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int v = acc[r][mt][c];
-                if (v != 0) atomicAdd(&red[(mt * 8 + 2 * q + (c & 1)) * kRedStride + 16 * r + g + 8 * (c >> 1)], v);
+                if (v != 0) atomicAdd(&red_w[(mt * 8 + 2 * q + (c & 1)) * kRedStride + 16 * r + g + 8 * (c >> 1)], v);
             }
     __syncthreads();
     phase_mark(6);
@@ -439,7 +445,7 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const Spm
         phase_mark(7);
         if (rank != 0) {
             const uint32_t remote = map_to_rank(sbase + L::red, 0);
-            for (int i = tid; i < MT * 8 * kRedStride; i += blockDim.x) {
+            for (int i = tid; i < rpc * MT * 8 * kRedStride; i += blockDim.x) {
                 const int v = red[i];
                 if (v != 0) red_add_cluster(remote + i * 4, v);
             }
@@ -452,10 +458,12 @@ __global__ void __launch_bounds__(MAXW * 32, MINB) spmm_small_m_kernel(const Spm
 
     // ---- epilogue (rank 0): scale and store
     const int N = p.N;
-    for (int i = tid; i < mrows * 64; i += blockDim.x) {
-        const int t = i >> 6, nl = i & 63;
-        const int n = rt * 64 + nl;
-        const int v = red[t * kRedStride + nl];
+    for (int i = tid; i < rpc * mrows * 64; i += blockDim.x) {
+        const int j = i >= mrows * 64 ? 1 : 0, r = i - j * mrows * 64;   // row tile of the CTA, index inside it
+        const int t = r >> 6, nl = r & 63;
+        const int n = ((int)blockIdx.y * rpc + j) * 64 + nl;
+        if (n >= N) continue;
+        const int v = red[j * (MT * 8 * kRedStride) + t * kRedStride + nl];
         const long long o = (long long)(m0 + t) * N + n;
         if (p.epilogue == EPI_RAW_I32) {
             reinterpret_cast<int*>(p.out)[o] = v;

@@ -53,6 +53,7 @@ static int device_sm_count() {
 //   TERNASPMM_PDL=0              launch without programmatic dependent launch
 //   TERNASPMM_FAT=0              small-batch kernel: never use the one-CTA-per-SM shape
 //   TERNASPMM_STAGE=0            small-batch kernel: no shared-memory slot for a warp's second tile
+//   TERNASPMM_RPC2=0             small-batch kernel: never put two row tiles into one fat CTA
 //   TERNASPMM_FORCE_S / _FORCE_W small-batch kernel: this K split and this many warps per CTA
 //   TERNASPMM_CTAS_PER_SM_X10    small-batch kernel, thin shape: about that many CTAs per SM (x10)
 //   TERNASPMM_MAX_WARPS          small-batch kernel, thin shape: cap on warps per CTA
@@ -61,7 +62,7 @@ static int device_sm_count() {
 //   TERNASPMM_LARGE_SPLIT=0      tcgen05 kernel without its cluster K split
 struct Tuning {
     int ctas_x10 = 0, max_warps = 0, pdl = 1, large_min_m = 33, large_split = 1, cluster_cost_x10 = 0, fat = 1,
-        force_s = 0, force_w = 0, stage = 1;
+        force_s = 0, force_w = 0, stage = 1, rpc2 = 1;
     Tuning() {
         if (const char* e = getenv("TERNASPMM_CTAS_PER_SM_X10")) ctas_x10 = atoi(e);
         if (const char* e = getenv("TERNASPMM_MAX_WARPS")) max_warps = atoi(e);
@@ -71,6 +72,7 @@ struct Tuning {
         if (const char* e = getenv("TERNASPMM_CLUSTER_COST_X10")) cluster_cost_x10 = atoi(e);
         if (const char* e = getenv("TERNASPMM_FAT")) fat = atoi(e);
         if (const char* e = getenv("TERNASPMM_STAGE")) stage = atoi(e) != 0;
+        if (const char* e = getenv("TERNASPMM_RPC2")) rpc2 = atoi(e) != 0;
         if (const char* e = getenv("TERNASPMM_FORCE_S")) force_s = atoi(e);
         if (const char* e = getenv("TERNASPMM_FORCE_W")) force_w = atoi(e);
     }
@@ -82,6 +84,7 @@ static const Tuning& tuning() {
 
 struct LaunchShape {
     int splits, warps;
+    int rpc = 1;   // row tiles per CTA (fat shape only)
 };
 
 // K split (= cluster size, at most 8) and warps per CTA.  Take the smallest
@@ -133,7 +136,11 @@ static LaunchShape choose_shape(int RT, int KT, int token_blocks, int max_warps,
 static LaunchShape choose_fat(int RT, int KT, int token_blocks, int max_warps, int mt) {
     const int sms = device_sm_count();
     const long long rows = (long long)RT * token_blocks;
-    if (!tuning().fat || rows > sms) return {0, 0};
+    if (!tuning().fat) return {0, 0};
+    // more row tiles than SMs, but at most twice as many: two row tiles per CTA, half of the warps each
+    if (rows > sms && token_blocks == 1 && RT % 2 == 0 && RT / 2 <= sms && tuning().rpc2)
+        return {1, max_warps & ~1, 2};
+    if (rows > sms) return {0, 0};
     const int max_s = KT > 1 ? (KT / 2 < 8 ? KT / 2 : 8) : 1;
     const int limit = mt >= 4 ? 3 : 2;
     int pick = 0;
@@ -150,7 +157,7 @@ static LaunchShape choose_fat(int RT, int KT, int token_blocks, int max_warps, i
 template <int MT, int MAXW, int MINB>
 static cudaError_t launch_small_m(SpmmParams& p, int token_blocks, int warp_slots, cudaStream_t stream,
                                   LaunchShape preset = {0, 0}) {
-    using L = SmallMSmem<MT>;
+    using L = SmallMSmem<MT, MINB == 1 ? 2 : 1>;
     static bool attr_done[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -162,7 +169,9 @@ static cudaError_t launch_small_m(SpmmParams& p, int token_blocks, int warp_slot
     // one CTA per SM (MINB == 1) leaves room for a 4 KB slot per warp: second tiles are decoded before the wait
     // (only the warps that have a second tile need one: the first nt - warps of them)
     const int nt = (p.K / 64 + shape.splits - 1) / shape.splits;
-    const int slots = (MINB == 1 && tuning().stage) ? std::max(0, std::min(warps, nt - warps)) : 0;
+    p.rpc = shape.rpc;
+    const int wpr = warps / shape.rpc;   // warps that share a row tile
+    const int slots = (MINB == 1 && tuning().stage && nt > wpr) ? (shape.rpc == 2 ? warps : std::min(warps, nt - warps)) : 0;
     p.stage_second = slots > 0 ? 1 : 0;
     const int smem_bytes = L::total + slots * 4096;
     if (!attr_done[dev]) {
@@ -173,7 +182,7 @@ static cudaError_t launch_small_m(SpmmParams& p, int token_blocks, int warp_slot
     }
     const int RT = p.N / 64;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(p.splits, RT, token_blocks);
+    cfg.gridDim = dim3(p.splits, RT / shape.rpc, token_blocks);
     cfg.blockDim = dim3(warps * 32, 1, 1);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
