@@ -110,9 +110,9 @@ class ClockSampler:
 # ----------------------------------------------------------------------------
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of spmm_small_m_kernel from one ncu capture of the
-# four layer shapes at full size (profiles/spmm_small_m_bitnet2b_sweep_M8.md: 1.991 + 1.346 + 7.018 + 3.573 MB),
+# four layer shapes at full size (profiles/spmm_small_m_bitnet2b_sweep_M8.md: 1.990 + 1.346 + 7.017 + 3.572 MB),
 # averaged like the step's launches (each shape once per layer); token count -> bytes.
-NCU_DRAM_BYTES_PER_LAUNCH = {8: (1.991e6 + 1.346e6 + 7.018e6 + 3.573e6) / 4}
+NCU_DRAM_BYTES_PER_LAUNCH = {8: (1.990e6 + 1.346e6 + 7.017e6 + 3.572e6) / 4}
 
 
 def cpu_sample(tokens, seconds_budget, seed=1234):
