@@ -148,7 +148,8 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    one_pass, alg, cores, reps, _ = cpu_sample(args.tokens, 4.0)
+    # a step = a bounded sample of the sweep (some passes over one layer); the whole run stays near a minute
+    one_pass, alg, cores, reps, _ = cpu_sample(args.tokens, max(0.1, 60.0 / max(1, args.steps)))
     for _ in range(args.warmup):
         one_pass()
     t0 = time.perf_counter()
