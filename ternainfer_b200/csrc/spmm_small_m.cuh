@@ -4,20 +4,27 @@
 // reduction/scale kernel (kernels/src/SpMM/SpMM_Kernel.cuh:16-163 and
 // kernels/src/SpMM/Reduction_Kernel.cuh:23-63 in Gu-J/TernaInfer).
 //
-// Work split: blockIdx.y = 64-row tile of the weight, blockIdx.x = K split
-// (the CTAs of one row tile form a thread-block cluster), blockIdx.z = block
-// of MT*8 tokens.  Every warp owns whole 64x64 tiles and runs decoupled from
-// the other warps: it streams its tiles' bitmap words (one coalesced 128-bit
-// load per lane), offsets and sign words from global memory through a
-// register pipeline (bitmaps two tiles ahead, sign words one tile ahead),
-// decodes them (bitmap popcount prefix -> sign windows -> two 256-entry
-// lookup tables of 4 int8 weights) straight into int8 MMA A fragments and
-// multiplies them with activation fragments read from L2.  The first tile of
-// every warp is decoded before the programmatic-dependency wait, since
-// weights never depend on the previous kernel.  Partial sums are combined
-// across warps in shared memory and across the cluster through distributed
-// shared memory; the cluster's first CTA applies the scale epilogue and
-// stores bf16.  The int32 workspace of the reference is not needed.
+// Work split: blockIdx.y = 64-row tile of the weight (or a pair of them, each
+// with half of the warps: fat CTAs for weights with more row tiles than SMs),
+// blockIdx.x = K split (the CTAs of one row tile form a thread-block
+// cluster), blockIdx.z = block of MT*8 tokens.  Every warp owns whole 64x64
+// tiles and runs decoupled from the other warps: it streams its tiles' bitmap
+// words (one coalesced 128-bit load per lane), offsets and sign words from
+// global memory through a register pipeline (bitmaps two tiles ahead, sign
+// words one tile ahead), decodes them (bitmap popcount prefix -> sign windows
+// -> two 256-entry lookup tables of 4 int8 weights) straight into int8 MMA A
+// fragments and multiplies them with activation fragments read from L2.  The
+// first tile of every warp is decoded into registers before the
+// programmatic-dependency wait, since weights never depend on the previous
+// kernel - and the second one into a per-warp shared-memory slot where the
+// launch has one CTA per SM.  Partial sums are combined across warps in
+// shared memory and across the cluster through distributed shared memory; the
+// cluster's first CTA applies the scale epilogue and stores bf16.  The int32
+// workspace of the reference is not needed.
+//
+// Template parameters: MT = token groups of 8 per pass, MAXW / MINB = launch
+// bounds (warps per CTA, CTAs per SM): <1,14,2> <2,10,2> <4,8,2> are the thin
+// variants (two CTAs per SM), <1,28,1> <2,20,1> <4,16,1> the fat ones.
 #pragma once
 #include <cuda_bf16.h>
 
