@@ -316,3 +316,15 @@ def test_cluster_k_split_of_the_tensor_core_kernel(lib, M, N, K, ws_num):
     assert (accumulate(lib, xq, Packed(w)) == c_oracle.ternaspmm(xq, w, np.full(M, 0x3F80, np.uint16),
                                                                np.full(4, 0x3F80, np.uint16), 1)[0]).all()
     assert lib.ternaspmm_last_status() == 0
+
+
+@pytest.mark.parametrize("M", [1, 8, 16, 32])
+@pytest.mark.parametrize("N,K", [(150 * 64, 64), (150 * 64, 320), (296 * 64, 192), (216 * 64, 1088)])
+def test_two_row_tiles_per_cta_shapes(lib, M, N, K):
+    """Between one and two row tiles per SM (an even count): the small-batch kernel puts two row tiles
+    into one fat CTA, half of the warps on each - also when a row tile has fewer k-tiles than warps."""
+    w = o.make_ternary(N, K, 0.45, seed=N + K + M)
+    xq = np.random.default_rng(M + K).integers(-128, 128, size=(M, K), dtype=np.int8)
+    assert (accumulate(lib, xq, Packed(w)) == o.gemm_i32(xq, w)).all()
+    assert lib.ternaspmm_last_status() == 0
+    check(lib, M, N, K, 2)
