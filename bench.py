@@ -442,10 +442,11 @@ def run_tp_arm(args):
         ones_d = torch.ones(dim // world, device=device)
         ones_f = torch.ones(ffn // world, device=device)
         layers.append((tp.ColumnParallelSpBitLinear(dim, specs[0][2], dic, "wqkv"),
-                       tp.RowParallelSpBitLinear(dim // world, dim, dic, "wo", None, ones_d, 1e-5, args.tp_mode),
+                       tp.RowParallelSpBitLinear(dim // world, dim, dic, "wo", None, ones_d, 1e-5, args.tp_mode,
+                                                 max_tokens=M),
                        tp.ColumnParallelSpBitLinear(dim, specs[2][2], dic, "w13"),
                        tp.RowParallelSpBitLinear(ffn // world, dim, dic, "w2", None, ones_f, 1e-5, args.tp_mode,
-                                                 gated=True)))
+                                                 gated=True, max_tokens=M)))
     gen.manual_seed(args.seed)
     x0 = torch.randn((M, dim), generator=gen, device=device).to(torch.bfloat16)
     attn = torch.randn((M, dim // world), generator=gen, device=device).to(torch.bfloat16)
@@ -514,13 +515,15 @@ def run_tp_arm(args):
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "int8xternary->int32->bf16", "data": "synthetic",
                 "config": {"workload": f"tp_linear_stack_8192x28672_bs{M}", "layers": L, "tokens": M, "tp": world,
-                           "row_parallel_mode": args.tp_mode, "collective": "one NCCL all-reduce per row-parallel linear"
-                           if args.tp_mode == "single" else "three all-reduces per row-parallel linear (bit-exact mode)",
+                           "row_parallel_mode": args.tp_mode,
+                           "collective": {"single": "one NCCL all-reduce per row-parallel linear",
+                                          "fused": "all-reduce inside the finish kernel over peer memory (plain NVLink loads)",
+                                          "exact": "three all-reduces per row-parallel linear (bit-exact mode)"}[args.tp_mode],
                            "l2_policy": "inputs larger than L2: %.0f MB of weights per step over all ranks" % (wb.item() / 1e6)},
                 "roofline": {"bound": "hbm", "achieved": val / world, "peak": peak, "unit": "GB/s",
                              "frac": val / world / peak, "peak_kind": "of " + kind, "traffic": None,
                              "note": "per-GPU compressed-weight bytes per second"},
-                "gpu_launches": (10 if args.tp_mode == "single" else 6) * L * args.steps, "clocks": clocks}
+                "gpu_launches": (6 if args.tp_mode == "exact" else 10) * L * args.steps, "clocks": clocks}
         print(json.dumps(line), flush=True)
     _finish(world)
 
@@ -652,7 +655,7 @@ def main():
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--workload", default="sweep", choices=["sweep", "tp", "decode"])
     ap.add_argument("--unfused", action="store_true", help="decode workload: plain torch glue between the linears")
-    ap.add_argument("--tp_mode", default="single", choices=["single", "exact"])
+    ap.add_argument("--tp_mode", default="single", choices=["single", "fused", "exact"])
     ap.add_argument("--no_graph", action="store_true", help="tp workload: launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--verbose", action="store_true")
     args = ap.parse_args()

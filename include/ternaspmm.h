@@ -175,6 +175,19 @@ void ternaspmm_partial_f32(int8_t* x, uint64_t* bitmap, int* tile_offsets, uint1
 void ternaspmm_tp_finish(float* buf, ternaspmm_bf16* ws, float eps, int full_width, int M, int N,
                          ternaspmm_bf16* residual, ternaspmm_bf16* out, ternaspmm_stream_t stream);
 
+/* The same tail with the all-reduce fused in, for one process per GPU with peer-mapped (symmetric)
+ * buffers: bufs[r] / flags[r] = rank r's partial buffer (fp32 [M*N] partials + [M] sums of squares,
+ * written by ternaspmm_partial_f32 / ternaspmm_scale_quant_sumsq) and flag array (uint32 [world],
+ * zero-initialised) as mapped in THIS process; counters = two local uint32 (zero-initialised) of this
+ * call site.  Every rank launches it once per call; it signals the peers, waits (bounded; status 4 when
+ * the limit runs out) until all of them have signalled, adds all partials in rank order with plain
+ * peer loads over NVLink and writes the finished bf16 rows.  Each call site needs its own buffers,
+ * flags and counters, and a step must contain at least two call sites (see act_quant.cuh). */
+void ternaspmm_tp_allreduce_finish(float** bufs, unsigned int** flags, int rank, int world,
+                                   unsigned int* counters, ternaspmm_bf16* ws, float eps, int full_width,
+                                   int M, int N, ternaspmm_bf16* residual, ternaspmm_bf16* out,
+                                   ternaspmm_stream_t stream);
+
 /* Host packer from int8 ternary [N][K] into caller-provided arrays
  * (bitmap N*K/64, tile_offsets tiles+1, quarter_offsets 3*tiles, sign_words
  * at least N*K/32 + 4 words, zero-filled by the call).  Returns the number of

@@ -147,4 +147,108 @@ __global__ void __launch_bounds__(256) tp_finish_kernel(const float* __restrict_
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Row-parallel tail with the all-reduce fused in (one process per GPU, peer memory over NVLink).
+// Every rank's fp32 partial outputs [M*N] and partial sums of squares [M] sit in a buffer that
+// all ranks have mapped (symmetric memory).  One launch per rank:
+//   1. block 0 tells every peer "my partials of this call are complete" by a system-scope atomic
+//      increment of this rank's counter in the peer's flag array (the partials were written by
+//      the previous kernel of the stream, so they are complete when this kernel starts);
+//   2. every block waits until all peers' counters in the LOCAL flag array have reached this
+//      call's number (runs so far + 1) - a bounded spin: after the limit the kernel reports
+//      ST_WAIT_TIMEOUT through `status` and writes nothing;
+//   3. every block pulls its slice of all ranks' partials with plain 16-byte loads (its own from
+//      local memory, the others over NVLink; no multicast), adds them in rank order - so every
+//      rank computes bit-identical sums - and applies rsqrt(sum_sq/width + eps) * ws (+ residual);
+//   4. the last block to finish advances the local run counter.
+// A rank may overwrite its partial buffer for the next call of the SAME call site only after
+// every peer has read it.  That holds when a step contains at least two such call sites with
+// buffers of their own (as a transformer layer does: O and down): passing the wait of the next
+// site proves that every peer has left the previous one.
+struct TpPeers {
+    const float* buf[8];      // partial buffers of ranks 0..world-1 (this rank's own pointer included)
+    unsigned int* flag[8];    // flag arrays of ranks 0..world-1: flag[r][j] = calls signalled by rank j
+};
+
+__global__ void __launch_bounds__(256) tp_allreduce_finish_kernel(const TpPeers peers, int rank, int world,
+                                                                  unsigned int* runs, unsigned int* done_blocks,
+                                                                  const __nv_bfloat16* ws, float eps, int full_width,
+                                                                  int M, int N, const __nv_bfloat16* residual,
+                                                                  __nv_bfloat16* out, int* status) {
+    __shared__ unsigned int expected_s;
+    __shared__ int failed_s;
+    griddep_launch_dependents();
+    griddep_wait();            // the partials come from the previous kernel of the stream
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        expected_s = *reinterpret_cast<volatile unsigned int*>(runs) + 1u;
+        failed_s = 0;
+    }
+    if (blockIdx.x == 0 && tid < world && tid != rank) {
+        __threadfence_system();
+        atomicAdd_system(peers.flag[tid] + rank, 1u);
+    }
+    __syncthreads();
+    const unsigned int expected = expected_s;
+    if (tid < world && tid != rank) {
+        const volatile unsigned int* f = peers.flag[rank] + tid;
+        bool ok = false;
+        for (unsigned int it = 0; it < (1u << 24); ++it) {
+            unsigned int v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if ((int)(v - expected) >= 0) {
+                ok = true;
+                break;
+            }
+            if (it > 64) __nanosleep(200);
+        }
+        if (!ok) failed_s = 1;
+    }
+    __syncthreads();
+    const bool failed = failed_s != 0;
+    if (failed && tid == 0) atomicExch(status, 4 /* ST_WAIT_TIMEOUT */);
+
+    if (!failed) {
+        const float w = __bfloat162float(ws[0]);
+        const long long total = (long long)M * N;          // N is a multiple of 4
+        for (long long i = ((long long)blockIdx.x * blockDim.x + tid) * 4; i < total;
+             i += (long long)gridDim.x * blockDim.x * 4) {
+            const int t = (int)(i / N);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            float ss = 0.f;
+            for (int r = 0; r < world; ++r) {
+                float4 v;
+                float q;
+                asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                             : "l"(peers.buf[r] + i));
+                asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(q) : "l"(peers.buf[r] + total + t));
+                acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+                ss += q;
+            }
+            const float rstd = rsqrtf(ss / (float)full_width + eps);
+            const float y[4] = {acc.x, acc.y, acc.z, acc.w};
+            __align__(8) __nv_bfloat16 o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                o[e] = __float2bfloat16_rn((y[e] * rstd) * w);
+                if (residual) o[e] = __float2bfloat16_rn(__bfloat162float(residual[i + e]) + __bfloat162float(o[e]));
+            }
+            *reinterpret_cast<uint2*>(out + i) = *reinterpret_cast<const uint2*>(o);
+        }
+    }
+    // the last block to get here closes the call
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        const unsigned int prev = atomicAdd(done_blocks, 1u);
+        if (prev == gridDim.x - 1) {
+            *done_blocks = 0u;
+            *reinterpret_cast<volatile unsigned int*>(runs) = expected;
+            __threadfence();
+        }
+    }
+}
+
 }  // namespace tsp

@@ -546,6 +546,49 @@ extern "C" void ternaspmm_tp_finish(float* buf, __nv_bfloat16* ws, float eps, in
     checkLastCudaError(__LINE__);
 }
 
+extern "C" void ternaspmm_tp_allreduce_finish(float** bufs, unsigned int** flags, int rank, int world,
+                                             unsigned int* counters, __nv_bfloat16* ws, float eps, int full_width,
+                                             int M, int N, __nv_bfloat16* residual, __nv_bfloat16* out,
+                                             cudaStream_t stream) {
+    t_host_status = ST_OK;
+    if (!bufs || !flags || !counters || !ws || !out || world < 1 || world > 8 || rank < 0 || rank >= world || M < 1 ||
+        N < 4 || (N % 4)) {
+        fprintf(stderr, "ternaspmm: tp_allreduce_finish: bad arguments (world 1..8, N a multiple of 4)\n");
+        t_host_status = ST_BAD_POINTER;
+        return;
+    }
+    TpPeers peers = {};
+    for (int r = 0; r < world; ++r) {
+        if (!bufs[r] || !flags[r]) {
+            t_host_status = ST_BAD_POINTER;
+            return;
+        }
+        peers.buf[r] = bufs[r];
+        peers.flag[r] = flags[r];
+    }
+    int* status = status_device_ptr();
+    if (!status) {
+        t_host_status = ST_LAUNCH;
+        return;
+    }
+    const long long vecs = ((long long)M * N + 3) / 4;
+    int blocks = (int)std::min<long long>((vecs + 255) / 256, 2ll * device_sm_count());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks, 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tuning().pdl ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, tp_allreduce_finish_kernel, peers, rank, world, counters, counters + 1,
+                           (const __nv_bfloat16*)ws, eps, full_width, M, N, (const __nv_bfloat16*)residual, out,
+                           status) != cudaSuccess)
+        t_host_status = ST_LAUNCH;
+    checkLastCudaError(__LINE__);
+}
+
 extern "C" int ternaspmm_last_status(void) {
     if (t_host_status != ST_OK) return t_host_status;
     int v = 0;

@@ -74,6 +74,8 @@ def load_library() -> ctypes.CDLL:
     lib.ternaspmm_partial_f32.restype = None
     lib.ternaspmm_tp_finish.argtypes = [_P, _P, ctypes.c_float, _I, _I, _I, _P, _P, _P]
     lib.ternaspmm_tp_finish.restype = None
+    lib.ternaspmm_tp_allreduce_finish.argtypes = [_P, _P, _I, _I, _P, _P, ctypes.c_float, _I, _I, _I, _P, _P, _P]
+    lib.ternaspmm_tp_allreduce_finish.restype = None
     lib.bitlinear_TernaSpMM_residual.argtypes = [_P] * 8 + [_I] * 4 + [_P, _P]
     lib.bitlinear_TernaSpMM_residual.restype = None
     lib.ternaspmm_pack_i8.argtypes = [_P, _I, _I, _P, _P, _P, _P]
@@ -90,6 +92,6 @@ EXPORTED_SYMBOLS = (
     "bitlinear_TernaSpMM", "bitlinear_TernaSpMM_decode", "bitlinear_TernaSpMM_prefill",
     "bitlinear_TernaSpMM_benchmark", "checkLastCudaError", "reorder_WT_h", "convert_reorderd",
     "gpu_sleep", "ternaspmm_last_status", "ternaspmm_accumulate_i32", "ternaspmm_linear_segments", "bitlinear_TernaSpMM_residual", "ternaspmm_quant",
-    "ternaspmm_scale_quant_sumsq", "ternaspmm_partial_f32", "ternaspmm_tp_finish", "ternaspmm_rmsnorm_quant", "ternaspmm_relu2_gate_rmsnorm_quant", "ternaspmm_pack_i8",
+    "ternaspmm_scale_quant_sumsq", "ternaspmm_partial_f32", "ternaspmm_tp_finish", "ternaspmm_tp_allreduce_finish", "ternaspmm_rmsnorm_quant", "ternaspmm_relu2_gate_rmsnorm_quant", "ternaspmm_pack_i8",
     "ternaspmm_unpack_i8", "ternaspmm_transcode_reference_layout",
 )

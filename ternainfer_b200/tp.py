@@ -20,6 +20,15 @@ cross-rank statistics.  Two modes:
     one also adding the residual stream).  Mathematically identical to the
     unsharded layer, numerically within bf16 rounding of it (each rank rounds
     with its own scale).
+``fused`` - the arithmetic of ``single`` with the collective inside the last
+    kernel: the partials land in a symmetric-memory buffer that every rank has
+    mapped (``torch.distributed._symmetric_memory``), and
+    ``ternaspmm_tp_allreduce_finish`` signals the peers, waits for them (bounded)
+    and pulls their partials over NVLink with plain loads while it applies the
+    RMS factor and weight scale.  Three launches per linear, no NCCL kernel.
+    Every rank adds the partials in rank order, so all ranks hold identical
+    activations.  Needs ``max_tokens`` at construction (buffer size) and at
+    least two such linears per step (see the kernel's header).
 ``exact`` - bit-identical to the unsharded layer: all-reduce the sum of
     squares, normalise, all-reduce (max) the absmax, quantise with the global
     scale, all-reduce the int32 accumulators, then apply the decode epilogue.
@@ -116,6 +125,32 @@ def _quant(x: torch.Tensor, amax: torch.Tensor = None):
     return (x * s).round().clamp(-128, 127).to(torch.int8), s
 
 
+class _PeerBuffers:
+    """One call site's symmetric memory: ``numel`` floats of partials followed by 8 uint32 flags,
+    mapped into every rank of ``group``, plus two local counters.  Construction is collective
+    (every rank must build its modules in the same order)."""
+
+    def __init__(self, numel: int, group, device):
+        import ctypes as C
+        import os
+        import torch.distributed._symmetric_memory as symm_mem
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer loads only
+        grp = group if group is not None else dist.group.WORLD
+        self.numel = numel
+        self.rank, self.world = dist.get_rank(grp), dist.get_world_size(grp)
+        total = (numel + 3) // 4 * 4 + 8                    # floats, then the flag words
+        self.local = symm_mem.empty(total, dtype=torch.float32, device=device)
+        self.local.zero_()
+        self.handle = symm_mem.rendezvous(self.local, grp)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        flag_off = 4 * ((numel + 3) // 4 * 4)
+        self.buf_ptrs = (C.c_void_p * self.world)(*ptrs)
+        self.flag_ptrs = (C.c_void_p * self.world)(*[p + flag_off for p in ptrs])
+        self.counters = torch.zeros(2, dtype=torch.int32, device=device)
+        torch.cuda.synchronize()
+        dist.barrier(group=grp)                             # every rank's flags are zero before the first call
+
+
 # ------------------------------------------------------------------ modules
 class ColumnParallelSpBitLinear(nn.Module):
     """Rows of a fused linear owned by this rank.  ``dic[key + '.weight_*']``
@@ -154,7 +189,8 @@ class RowParallelSpBitLinear(nn.Module):
     on the GPU only)."""
 
     def __init__(self, in_features: int, out_features: int, dic: dict, key: str, group=None,
-                 norm_weight: torch.Tensor = None, eps: float = 1e-5, mode: str = "single", gated: bool = False):
+                 norm_weight: torch.Tensor = None, eps: float = 1e-5, mode: str = "single", gated: bool = False,
+                 max_tokens: int = 0):
         super().__init__()
         self.in_features, self.out_features = in_features, out_features
         dev = "cuda" if torch.cuda.is_available() else "cpu"
@@ -167,6 +203,10 @@ class RowParallelSpBitLinear(nn.Module):
         self.group, self.eps, self.mode, self.gated = group, eps, mode, gated
         self.tp = dist.get_world_size(group) if dist.is_initialized() else 1
         self.fused = True       # False: the torch formulation of the same arithmetic (tests compare the two)
+        self._peer = None
+        if mode == "fused":
+            assert max_tokens > 0, "the fused collective needs max_tokens (size of the symmetric buffer)"
+            self._peer = _PeerBuffers(max_tokens * out_features + max_tokens, group, dev)
 
     def _forward_fused(self, x2: torch.Tensor, residual):
         """GPU path of the ``single`` mode: three launches around one all-reduce."""
@@ -189,9 +229,34 @@ class RowParallelSpBitLinear(nn.Module):
                                 residual.data_ptr() if residual is not None else None, out.data_ptr(), st)
         return out
 
+    def _forward_peer(self, x2: torch.Tensor, residual):
+        """``fused`` mode: partials into the symmetric buffer, collective inside the finish kernel."""
+        lib = load_library()
+        M, K, N = x2.shape[0], self.in_features, self.out_features
+        pb = self._peer
+        assert M * N + M <= pb.numel, "more tokens than max_tokens"
+        dev = x2.device
+        xq = torch.empty((M, K), dtype=torch.int8, device=dev)
+        s = torch.empty((M,), dtype=torch.bfloat16, device=dev)
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        cv, tg, tm, bm = self.packed
+        st = _stream()
+        base = pb.local.data_ptr()
+        lib.ternaspmm_scale_quant_sumsq(x2.data_ptr(), self.norm_weight_bf16.data_ptr(), int(self.gated), M, K,
+                                        xq.data_ptr(), s.data_ptr(), base + 4 * M * N, st)
+        lib.ternaspmm_partial_f32(xq.data_ptr(), bm.data_ptr(), tg.data_ptr(), tm.data_ptr(), cv.data_ptr(),
+                                  base, s.data_ptr(), M, N, K, st)
+        lib.ternaspmm_tp_allreduce_finish(pb.buf_ptrs, pb.flag_ptrs, pb.rank, pb.world, pb.counters.data_ptr(),
+                                          self.ws_bf16.data_ptr(), self.eps, K * self.tp, M, N,
+                                          residual.data_ptr() if residual is not None else None, out.data_ptr(), st)
+        return out
+
     def forward(self, x, residual=None):
         shape = list(x.shape[:-1]) + [self.out_features]
         x2 = x.reshape(-1, self.in_features * (2 if self.gated else 1))
+        if self.mode == "fused":
+            res2 = residual.reshape(-1, self.out_features).contiguous() if residual is not None else None
+            return self._forward_peer(x2.contiguous(), res2).reshape(shape)
         if self.fused and self.mode == "single" and x2.is_cuda and x2.dtype == torch.bfloat16:
             res2 = residual.reshape(-1, self.out_features).contiguous() if residual is not None else None
             return self._forward_fused(x2.contiguous(), res2).reshape(shape)
