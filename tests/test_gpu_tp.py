@@ -123,3 +123,88 @@ def test_two_emulated_k_shards_against_unsharded_layer(lib):
     # quantisation noise of int8 activations: ~0.4 % of the row's output RMS per element
     assert err.max().item() <= 0.05 * want.abs().max().item()
     assert (err.pow(2).mean().sqrt() / want.pow(2).mean().sqrt()).item() < 0.02
+
+
+def test_allreduce_finish_kernel_with_one_rank(lib):
+    """World size 1: the fused tail degenerates to the plain finish kernel (no peer to wait for);
+    two calls in a row exercise the run counter."""
+    import ctypes as C
+    M, N, W = 24, 1024, 4096
+    g = torch.Generator(device="cuda").manual_seed(3)
+    buf = torch.randn(M * N + M, generator=g, device="cuda")
+    buf[M * N:] = buf[M * N:].abs() * W
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    counters = torch.zeros(2, dtype=torch.int32, device="cuda")
+    ws = torch.tensor([0.03]).to(torch.bfloat16).cuda()
+    res = torch.randn((M, N), generator=g, device="cuda").to(torch.bfloat16)
+    want = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    got = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    lib.ternaspmm_tp_finish(buf.data_ptr(), ws.data_ptr(), 1e-5, W, M, N, res.data_ptr(), want.data_ptr(), st)
+    bufs, flg = (C.c_void_p * 1)(buf.data_ptr()), (C.c_void_p * 1)(flags.data_ptr())
+    for call in range(2):
+        got.zero_()
+        lib.ternaspmm_tp_allreduce_finish(bufs, flg, 0, 1, counters.data_ptr(), ws.data_ptr(), 1e-5, W, M, N,
+                                          res.data_ptr(), got.data_ptr(), st)
+        torch.cuda.synchronize()
+        assert lib.ternaspmm_last_status() == 0
+        assert torch.equal(got, want)
+        assert counters.tolist() == [call + 1, 0]
+
+
+def _two_rank_worker(rank, world, port, ok):
+    import os
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    from ternainfer_b200 import tp
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", device_id=dev)
+    K, N, M = 2048, 1024, 40
+    g = torch.Generator(device=dev).manual_seed(11)
+    w = ternary(N, K, 5)
+    nw = (1 + 0.1 * torch.randn(K, generator=g, device=dev)).to(torch.bfloat16)
+    x = torch.randn((M, K), generator=g, device=dev).to(torch.bfloat16)
+    res = torch.randn((M, N), generator=g, device=dev).to(torch.bfloat16)
+
+    def make(mode):
+        dic = {}
+        tp.shard_checkpoint_entry(dic, "l", w, torch.tensor([0.03, 0, 0, 0]).to(torch.bfloat16), None, "row", rank, world)
+        return tp.RowParallelSpBitLinear(K // world, N, dic, "l", None, tp.shard_vector(nw, rank, world), 1e-5, mode,
+                                         max_tokens=M)
+
+    a, b, c = make("single"), make("fused"), make("fused")
+    xs = x[:, rank * (K // world):(rank + 1) * (K // world)].contiguous()
+    ya = a(xs, residual=res)
+    good = True
+    for _ in range(3):
+        yb, yc = b(xs, residual=res), c(xs, residual=res)
+        good = good and torch.equal(ya, yb) and torch.equal(yb, yc)
+    torch.cuda.synchronize()
+    ok[rank] = int(good and load_ok())
+    dist.barrier()
+    torch.cuda.synchronize()
+    os._exit(0)
+
+
+def load_ok():
+    from ternainfer_b200 import load_library
+    return load_library().ternaspmm_last_status() == 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_collective_matches_nccl_on_two_gpus(lib):
+    """Two ranks, one per GPU: the finish kernel with the all-reduce over peer memory gives the same
+    bits as the NCCL all-reduce followed by the plain finish kernel, on both of two call sites."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    ok = ctx.Array("i", [0, 0])
+    procs = [ctx.Process(target=_two_rank_worker, args=(r, 2, 29577, ok)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=180)
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+    assert list(ok) == [1, 1]
