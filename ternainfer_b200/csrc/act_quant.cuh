@@ -194,7 +194,7 @@ __global__ void __launch_bounds__(256) tp_allreduce_finish_kernel(const TpPeers 
     if (tid < world && tid != rank) {
         const volatile unsigned int* f = peers.flag[rank] + tid;
         bool ok = false;
-        for (unsigned int it = 0; it < (1u << 24); ++it) {
+        for (unsigned int it = 0; it < (1u << 22); ++it) {   // about a second at most
             unsigned int v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
             if ((int)(v - expected) >= 0) {
