@@ -23,8 +23,11 @@
  * convert_reorderd() / the Python packer, not the reference's mma.m16n8k16
  * order.  ternaspmm_transcode_reference_layout() converts arrays packed by the
  * reference's packer.  Requirements: N % 64 == 0, K % 64 == 0, M >= 1,
- * x / bitmap / sign_words 16-byte aligned, sign_words readable up to the next
- * 16-byte boundary after its last word.
+ * x / bitmap / sign_words 16-byte aligned, and sign_words readable for two
+ * words (8 bytes) past its last word tile_offsets[last]/32 - 1: the kernels
+ * fetch a lane's sign window as a pair of words without looking at its length.
+ * (The reference's own caller allocates 32 spare bytes, tests/test_kernel.cu:
+ * 257-288; the packers of this library pad 4 words.)
  */
 #ifndef TERNASPMM_H_
 #define TERNASPMM_H_
@@ -107,10 +110,28 @@ void gpu_sleep(double sleep_us, ternaspmm_stream_t stream);
 /* ---- additions (no counterpart in the reference) ------------------------ */
 
 /* Status of the most recent compute call on this thread's device: 0 = ok,
- * 1 = bad shape, 2 = bad pointer/alignment, 3 = launch failure, 4 = a device
- * wait on a bulk copy ran out (kernel returned early).  Reading the device
- * word synchronises the device; do not call while capturing. */
+ * 1 = bad shape, 2 = bad pointer/alignment, 3 = launch failure (also a failed
+ * tensor-map encode: nothing was launched), 4 = a bounded device-side wait ran
+ * out (an mbarrier hand-off inside the tensor-core kernel, or a peer's signal
+ * in the fused tensor-parallel tail) and the kernel returned early.  Reading
+ * the device word synchronises the device; do not call while capturing. */
 int ternaspmm_last_status(void);
+
+/* Limit of the device-side wait for a peer's signal in
+ * ternaspmm_tp_allreduce_finish, in milliseconds of the GPU's global timer
+ * (default 1000, clamped to 1..10000).  Process-wide. */
+void ternaspmm_set_wait_limit_ms(int ms);
+
+/* Test hook: shape of the most recent kernel launch made by this thread.
+ * out6 = {kernel (1 = small-batch kernel, one fat CTA per SM; 2 = small-batch
+ * kernel, thin CTAs; 3 = tcgen05 kernel), tokens per pass, K split (cluster
+ * size), warps per CTA, 64-row tiles per CTA, CTAs}. */
+void ternaspmm_last_launch_shape(int* out6);
+
+/* Test hook (host-side fault injection): kind 1 makes the next tensor-map
+ * encode of this thread report failure, so the call ends with status 3
+ * without launching anything. */
+void ternaspmm_debug_inject_host_failure(int kind);
 
 /* Test hook: same contraction, raw int32 accumulators out[M][N]. */
 void ternaspmm_accumulate_i32(int8_t* x, uint64_t* bitmap, int* tile_offsets,
@@ -176,16 +197,20 @@ void ternaspmm_tp_finish(float* buf, ternaspmm_bf16* ws, float eps, int full_wid
                          ternaspmm_bf16* residual, ternaspmm_bf16* out, ternaspmm_stream_t stream);
 
 /* The same tail with the all-reduce fused in, for one process per GPU with peer-mapped (symmetric)
- * buffers: bufs[r] / flags[r] = rank r's partial buffer (fp32 [M*N] partials + [M] sums of squares,
- * written by ternaspmm_partial_f32 / ternaspmm_scale_quant_sumsq) and flag array (uint32 [world],
- * zero-initialised) as mapped in THIS process; counters = two local uint32 (zero-initialised) of this
- * call site.  Every rank launches it once per call; it signals the peers, waits (bounded; status 4 when
- * the limit runs out) until all of them have signalled, adds all partials in rank order with plain
- * peer loads over NVLink and writes the finished bf16 rows.  Each call site needs its own buffers,
- * flags and counters, and a step must contain at least two call sites (see act_quant.cuh). */
-void ternaspmm_tp_allreduce_finish(float** bufs, unsigned int** flags, int rank, int world,
-                                   unsigned int* counters, ternaspmm_bf16* ws, float eps, int full_width,
-                                   int M, int N, ternaspmm_bf16* residual, ternaspmm_bf16* out,
+ * buffers.  bufs[r] / flags[r] / outs[r] = rank r's partial buffer (fp32 [M*N] partials + [M] sums
+ * of squares, written by ternaspmm_partial_f32 / ternaspmm_scale_quant_sumsq), flag array (uint32
+ * [16], zero-initialised once) and bf16 output buffer [M*N], as mapped in THIS process; counters =
+ * two local uint32 (zero-initialised) of this call site.  Every rank launches it once per call.  It
+ * signals the peers, waits until all of them have signalled, reduces ITS slice of the outputs over
+ * all ranks' partials (plain peer loads over NVLink, rank order), applies the RMS factor, ws[0] and
+ * the optional residual, pushes the finished bf16 slice into every rank's output buffer (plain peer
+ * stores), and returns only after every peer's slice has arrived: the result is outs[rank].  All
+ * waits are bounded (ternaspmm_set_wait_limit_ms); when one runs out, status 4 is recorded and
+ * outs[rank] is filled with bf16 NaN.  Each call site needs its own buffers, flags and counters; a
+ * call site's buffers may be reused by its next call without any further synchronisation. */
+void ternaspmm_tp_allreduce_finish(float** bufs, unsigned int** flags, ternaspmm_bf16** outs, int rank,
+                                   int world, unsigned int* counters, ternaspmm_bf16* ws, float eps,
+                                   int full_width, int M, int N, ternaspmm_bf16* residual,
                                    ternaspmm_stream_t stream);
 
 /* Host packer from int8 ternary [N][K] into caller-provided arrays

@@ -4,7 +4,14 @@ Follows ``convert/convert_TernaInfer.py`` of Gu-J/TernaInfer: absmean
 ternarisation per scale segment with 4-slot bf16 scale vectors (:153-199),
 one packed weight = four tensors under ``<key>_compressed_val`` /
 ``_TileOffsets_global`` / ``_TileOffsets_median`` / ``_bitmap`` (:201-209) and
-three output files (:238, :267-268).  The packing itself is
+three output files (:238, :267-268): ``model_bf16.pt`` (the de-quantised dense
+comparator, :111-150), ``model_TernaInfer_TernaryWeights.pt`` and
+``model_embeddings_and_norms_non_ternary.pt``.  One addition: next to every
+``weight_scale`` vector the lengths of its scale segments are stored as
+``weight_segments`` (int64), so that the call site can pass explicit segment
+boundaries instead of relying on the reference's built-in rule (equal widths,
+or 2560/640/640 when there are 3840 outputs), which is wrong for any other
+grouped-query shape.  The packing itself is
 ``convert_utils.compress_weight`` (B200 tile order, vectorised, optionally on
 the GPU), so no process pool is needed.  Input is a state dict with the
 reference's fused names (``layers.N.attention.wqkv.weight`` ...); the
@@ -29,21 +36,45 @@ def quant_weight_int8(weight: torch.Tensor):
     return new_weight, (1.0 / s).to(torch.bfloat16).reshape(1)
 
 
+def _segments(key: str, value: torch.Tensor, dim: int, n_heads: int, n_kv_heads: int, ffn_dim: int):
+    """Row blocks of a fused weight that get a scale of their own (convert_TernaInfer.py:168-194
+    of the reference), or None for tensors that are not ternary linears."""
+    head_dim = dim // n_heads
+    if "wqkv" in key:
+        kv = head_dim * n_kv_heads
+        return [value[:dim], value[dim:dim + kv], value[dim + kv:]]
+    if "w13" in key:
+        return [value[:ffn_dim], value[ffn_dim:]]
+    if "w2" in key or "wo" in key:
+        return [value]
+    return None
+
+
+def dequantise_state_dict(state: Dict[str, torch.Tensor], dim: int, n_heads: int, n_kv_heads: int, ffn_dim: int):
+    """The dense comparator's weights (convert_TernaInfer.py:111-150 of the reference): every
+    segment ternarised and multiplied back by its scale, other tensors copied."""
+    out = {}
+    for key, value in state.items():
+        parts = _segments(key, value, dim, n_heads, n_kv_heads, ffn_dim)
+        if parts is None:
+            out[key] = value.clone()
+            continue
+        deq = []
+        for p in parts:
+            s = 1.0 / p.abs().mean().clamp_(min=1e-5)
+            deq.append((p * s).round().clamp(-1, 1) / s)
+        out[key] = torch.cat(deq, dim=0)
+    return out
+
+
 def ternarise_state_dict(state: Dict[str, torch.Tensor], dim: int, n_heads: int, n_kv_heads: int, ffn_dim: int):
     """Fused bf16/fp32 weights -> int8 ternary + ``weight_scale`` vectors
-    [q,k,v,0] / [gate,up,0,0] / [w,0,0,0]."""
+    [q,k,v,0] / [gate,up,0,0] / [w,0,0,0] (+ ``weight_segments``: the segment lengths)."""
     out = {}
     zero = torch.zeros(1, dtype=torch.bfloat16)
-    head_dim = dim // n_heads
     for key, value in state.items():
-        if "wqkv" in key:
-            kv = head_dim * n_kv_heads
-            parts = [value[:dim], value[dim:dim + kv], value[dim + kv:]]
-        elif "w13" in key:
-            parts = [value[:ffn_dim], value[ffn_dim:]]
-        elif "w2" in key or "wo" in key:
-            parts = [value]
-        else:
+        parts = _segments(key, value, dim, n_heads, n_kv_heads, ffn_dim)
+        if parts is None:
             if "output.weight" not in key:
                 out[key] = value.clone()
             continue
@@ -51,6 +82,7 @@ def ternarise_state_dict(state: Dict[str, torch.Tensor], dim: int, n_heads: int,
         out[key] = torch.cat([w for w, _ in q], dim=0)
         scales = [s.cpu() for _, s in q] + [zero] * (4 - len(q))
         out[key.replace("weight", "weight_scale")] = torch.cat(scales, dim=0)
+        out[key.replace("weight", "weight_segments")] = torch.tensor([p.shape[0] for p in parts], dtype=torch.int64)
     return out
 
 
@@ -131,9 +163,11 @@ def main():
         state = load_file(a.input)
     else:
         state = torch.load(a.input, map_location="cpu")
+    os.makedirs(a.output_dir, exist_ok=True)
+    torch.save(dequantise_state_dict(state, a.dim, a.n_heads, a.n_kv_heads, a.ffn_dim),
+               os.path.join(a.output_dir, "model_bf16.pt"))
     int8_state = ternarise_state_dict(state, a.dim, a.n_heads, a.n_kv_heads, a.ffn_dim)
     ternary, other = pack_state_dict(int8_state, a.device)
-    os.makedirs(a.output_dir, exist_ok=True)
     torch.save(ternary, os.path.join(a.output_dir, "model_TernaInfer_TernaryWeights.pt"))
     torch.save(other, os.path.join(a.output_dir, "model_embeddings_and_norms_non_ternary.pt"))
     print(f"saved {len(ternary) // 4} packed weights to {a.output_dir}")

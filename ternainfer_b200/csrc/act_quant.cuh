@@ -149,35 +149,60 @@ __global__ void __launch_bounds__(256) tp_finish_kernel(const float* __restrict_
 
 
 // ---------------------------------------------------------------------------------------------
-// Row-parallel tail with the all-reduce fused in (one process per GPU, peer memory over NVLink).
+// Row-parallel tail with the all-reduce fused in (one process per GPU, peer memory over NVLink),
+// as a reduce-scatter followed by an all-gather inside ONE launch per rank.
 // Every rank's fp32 partial outputs [M*N] and partial sums of squares [M] sit in a buffer that
-// all ranks have mapped (symmetric memory).  One launch per rank:
+// all ranks have mapped (symmetric memory), and so does every rank's bf16 output [M*N].
 //   1. block 0 tells every peer "my partials of this call are complete" by a system-scope atomic
 //      increment of this rank's counter in the peer's flag array (the partials were written by
 //      the previous kernel of the stream, so they are complete when this kernel starts);
 //   2. every block waits until all peers' counters in the LOCAL flag array have reached this
-//      call's number (runs so far + 1) - a bounded spin: after the limit the kernel reports
-//      ST_WAIT_TIMEOUT through `status` and writes nothing;
-//   3. every block pulls its slice of all ranks' partials with plain 16-byte loads (its own from
-//      local memory, the others over NVLink; no multicast), adds them in rank order - so every
-//      rank computes bit-identical sums - and applies rsqrt(sum_sq/width + eps) * ws (+ residual);
-//   4. the last block to finish advances the local run counter.
-// A rank may overwrite its partial buffer for the next call of the SAME call site only after
-// every peer has read it.  That holds when a step contains at least two such call sites with
-// buffers of their own (as a transformer layer does: O and down): passing the wait of the next
-// site proves that every peer has left the previous one.
+//      call's number (runs so far + 1) - a spin bounded by `limit_ns` of the global timer;
+//   3. rank r owns the r-th slice of the M*N outputs: its blocks pull that slice of all ranks'
+//      partials with plain 16-byte loads (own from local memory, the others over NVLink; no
+//      multicast), add them in rank order, apply rsqrt(sum_sq/width + eps) * ws (+ residual) and
+//      push the finished bf16 values into EVERY rank's output buffer with plain peer stores.
+//      Per rank (T-1)/T * (4 + 2) * M*N bytes cross NVLink instead of (T-1) * 4 * M*N for
+//      "every rank pulls everything"; each output element is computed once, so all ranks hold
+//      bit-identical activations;
+//   4. the last block of the rank to finish signals "my slice has been pushed and I have read
+//      your partials" to every peer (second counter set), waits (bounded) for the same signal
+//      from all peers and advances the local run counter.  When the kernel ends, this rank's
+//      output is complete AND no peer still reads this rank's partial buffer, so the buffers of
+//      a call site may be reused by the very next call: no ordering rule is left to the caller.
+// When a wait runs out the kernel reports ST_WAIT_TIMEOUT through `status`, fills its own output
+// with bf16 NaN (a missed peer shows up downstream instead of as stale data) and returns.
 struct TpPeers {
     const float* buf[8];      // partial buffers of ranks 0..world-1 (this rank's own pointer included)
-    unsigned int* flag[8];    // flag arrays of ranks 0..world-1: flag[r][j] = calls signalled by rank j
+    unsigned int* flag[8];    // flag arrays of ranks 0..world-1: flag[r][j] = "partials ready" calls signalled by
+                              // rank j, flag[r][8 + j] = "slice pushed" calls signalled by rank j
+    __nv_bfloat16* out[8];    // output buffers of ranks 0..world-1
 };
+
+// Bounded wait until *f (system scope) has reached `expected`.
+__device__ __forceinline__ bool wait_counter_sys(const volatile unsigned int* f, unsigned int expected,
+                                                 unsigned long long limit_ns) {
+    const unsigned long long t_start = global_timer_ns();
+    for (unsigned int it = 0; it < (1u << 26); ++it) {   // wall-time limit below; the count is a second fence
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+        if ((int)(v - expected) >= 0) return true;
+        if (it > 64) {
+            __nanosleep(200);
+            if (global_timer_ns() - t_start > limit_ns) return false;
+        }
+    }
+    return false;
+}
 
 __global__ void __launch_bounds__(256) tp_allreduce_finish_kernel(const TpPeers peers, int rank, int world,
                                                                   unsigned int* runs, unsigned int* done_blocks,
                                                                   const __nv_bfloat16* ws, float eps, int full_width,
                                                                   int M, int N, const __nv_bfloat16* residual,
-                                                                  __nv_bfloat16* out, int* status) {
+                                                                  int* status, unsigned long long limit_ns) {
     __shared__ unsigned int expected_s;
     __shared__ int failed_s;
+    __shared__ int last_s;
     griddep_launch_dependents();
     griddep_wait();            // the partials come from the previous kernel of the stream
     const int tid = threadIdx.x;
@@ -191,29 +216,18 @@ __global__ void __launch_bounds__(256) tp_allreduce_finish_kernel(const TpPeers 
     }
     __syncthreads();
     const unsigned int expected = expected_s;
-    if (tid < world && tid != rank) {
-        const volatile unsigned int* f = peers.flag[rank] + tid;
-        bool ok = false;
-        for (unsigned int it = 0; it < (1u << 22); ++it) {   // about a second at most
-            unsigned int v;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-            if ((int)(v - expected) >= 0) {
-                ok = true;
-                break;
-            }
-            if (it > 64) __nanosleep(200);
-        }
-        if (!ok) failed_s = 1;
-    }
+    if (tid < world && tid != rank && !wait_counter_sys(peers.flag[rank] + tid, expected, limit_ns)) failed_s = 1;
     __syncthreads();
     const bool failed = failed_s != 0;
-    if (failed && tid == 0) atomicExch(status, 4 /* ST_WAIT_TIMEOUT */);
+    __nv_bfloat16* out = peers.out[rank];
+    const long long total = (long long)M * N;          // N is a multiple of 4
+    const long long vecs = total >> 2;
 
     if (!failed) {
         const float w = __bfloat162float(ws[0]);
-        const long long total = (long long)M * N;          // N is a multiple of 4
-        for (long long i = ((long long)blockIdx.x * blockDim.x + tid) * 4; i < total;
-             i += (long long)gridDim.x * blockDim.x * 4) {
+        const long long v0 = vecs * rank / world, v1 = vecs * (rank + 1) / world;   // this rank's slice
+        for (long long vi = v0 + (long long)blockIdx.x * blockDim.x + tid; vi < v1; vi += (long long)gridDim.x * blockDim.x) {
+            const long long i = vi << 2;
             const int t = (int)(i / N);
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             float ss = 0.f;
@@ -235,19 +249,44 @@ __global__ void __launch_bounds__(256) tp_allreduce_finish_kernel(const TpPeers 
                 o[e] = __float2bfloat16_rn((y[e] * rstd) * w);
                 if (residual) o[e] = __float2bfloat16_rn(__bfloat162float(residual[i + e]) + __bfloat162float(o[e]));
             }
-            *reinterpret_cast<uint2*>(out + i) = *reinterpret_cast<const uint2*>(o);
+            const uint2 packed = *reinterpret_cast<const uint2*>(o);
+            for (int r = 0; r < world; ++r) *reinterpret_cast<uint2*>(peers.out[r] + i) = packed;   // all-gather by push
         }
+    } else {
+        if (tid == 0) atomicExch(status, 4 /* ST_WAIT_TIMEOUT */);
+        for (long long vi = (long long)blockIdx.x * blockDim.x + tid; vi < vecs; vi += (long long)gridDim.x * blockDim.x)
+            *reinterpret_cast<uint2*>(out + (vi << 2)) = make_uint2(0x7FC07FC0u, 0x7FC07FC0u);
     }
-    // the last block to get here closes the call
+
+    // the last block of this rank to get here closes the call
+    __threadfence_system();    // this thread's pushes are visible system-wide before the block is counted
     __syncthreads();
     if (tid == 0) {
-        __threadfence();
         const unsigned int prev = atomicAdd(done_blocks, 1u);
-        if (prev == gridDim.x - 1) {
-            *done_blocks = 0u;
-            *reinterpret_cast<volatile unsigned int*>(runs) = expected;
-            __threadfence();
+        last_s = prev == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!last_s) return;
+    __threadfence_system();
+    if (tid < world && tid != rank) {
+        bool ok = true;
+        if (!failed) {
+            atomicAdd_system(peers.flag[tid] + 8 + rank, 1u);       // my slice sits in your output; I am done with your partials
+            ok = wait_counter_sys(peers.flag[rank] + 8 + tid, expected, limit_ns);
         }
+        if (!ok) failed_s = 2;
+    }
+    __syncthreads();
+    if (failed_s == 2) {
+        // a peer's slice never arrived: the whole output is suspect
+        if (tid == 0) atomicExch(status, 4 /* ST_WAIT_TIMEOUT */);
+        for (long long vi = tid; vi < vecs; vi += blockDim.x)
+            *reinterpret_cast<uint2*>(out + (vi << 2)) = make_uint2(0x7FC07FC0u, 0x7FC07FC0u);
+    }
+    if (tid == 0) {
+        *done_blocks = 0u;
+        *reinterpret_cast<volatile unsigned int*>(runs) = expected;
+        __threadfence();
     }
 }
 

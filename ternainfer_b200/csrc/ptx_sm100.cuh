@@ -1,7 +1,7 @@
-// Thin inline-PTX wrappers used by the sm_100a kernels: mbarrier with bounded
-// waits, 1-D bulk async copies (TMA engine, no multicast), cluster barriers,
-// the int8 tensor-core MMA used on the small-batch path, and shared-memory
-// vector accesses by 32-bit shared address.
+// Thin inline-PTX wrappers used by the sm_100a kernels: mbarrier primitives,
+// cluster barriers and distributed shared memory, programmatic dependent
+// launch, the int8 tensor-core MMA used on the small-batch path, coherent
+// global loads, and shared-memory vector accesses by 32-bit shared address.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -19,9 +19,6 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_fence_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(bar) : "memory");
 }
@@ -38,26 +35,6 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Wait for a phase with an iteration limit (roughly half a second): a wrong
-// byte count or a lost copy must end the kernel with an error status, never
-// spin forever.  Returns false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-    for (uint32_t it = 0; it < (1u << 22); ++it) {
-        if (mbar_test(bar, parity)) return true;
-        if (it > 64) __nanosleep(64);
-    }
-    return false;
-}
-
-// ------------------------------------------------------- bulk async copy
-// global -> shared::cta, completion counted in bytes on an mbarrier.  Both
-// addresses 16-byte aligned, size a multiple of 16.  No multicast.
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
-
 // -------------------------------------------------------- cluster barrier
 __device__ __forceinline__ void cluster_arrive() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -83,6 +60,23 @@ __device__ __forceinline__ void red_add_cluster(uint32_t cluster_addr, int v) {
 // ------------------------------------------- programmatic dependent launch
 __device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// ------------------------------------------------------ coherent global loads
+// Data written by the previous kernel of the stream (activations, scales,
+// residuals) is read through L2 with ld.global.cg: under programmatic dependent
+// launch this kernel is already resident while the producer still writes, and
+// the read-only (.nc) path is only defined for data that never changes during
+// the kernel's lifetime.  Immutable weight streams keep __ldg.
+__device__ __forceinline__ uint4 ld_cg_128(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 // ----------------------------------------------------- shared vector access
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {

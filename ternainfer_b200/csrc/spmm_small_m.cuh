@@ -299,8 +299,8 @@ __device__ __forceinline__ void load_x_frags(uint4 (&bx)[MT], const int8_t* x, i
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
         const int t = mt * 8 + g;
-        bx[mt] = t < mrows ? __ldg(reinterpret_cast<const uint4*>(x + (long long)(m0 + t) * K + ktile * 64 + q * 16))
-                           : make_uint4(0, 0, 0, 0);
+        // produced by the previous kernel of the stream: coherent load through L2, not the read-only path
+        bx[mt] = t < mrows ? ld_cg_128(x + (long long)(m0 + t) * K + ktile * 64 + q * 16) : make_uint4(0, 0, 0, 0);
     }
 }
 

@@ -49,8 +49,8 @@ static int device_sm_count() {
     return sms[dev];
 }
 
-// Launch-shape knobs, read once from the environment (for tuning runs; the defaults are the product):
-//   TERNASPMM_PDL=0              launch without programmatic dependent launch
+// Launch-shape knobs.  The product reads ONE environment variable, TERNASPMM_PDL=0 (launch without
+// programmatic dependent launch).  The others exist only in tuning builds (-DTSP_TUNING):
 //   TERNASPMM_FAT=0              small-batch kernel: never use the one-CTA-per-SM shape
 //   TERNASPMM_STAGE=0            small-batch kernel: no shared-memory slot for a warp's second tile
 //   TERNASPMM_RPC2=0             small-batch kernel: never put two row tiles into one fat CTA
@@ -64,9 +64,10 @@ struct Tuning {
     int ctas_x10 = 0, max_warps = 0, pdl = 1, large_min_m = 33, large_split = 1, cluster_cost_x10 = 0, fat = 1,
         force_s = 0, force_w = 0, stage = 1, rpc2 = 1;
     Tuning() {
+        if (const char* e = getenv("TERNASPMM_PDL")) pdl = atoi(e) != 0;
+#ifdef TSP_TUNING
         if (const char* e = getenv("TERNASPMM_CTAS_PER_SM_X10")) ctas_x10 = atoi(e);
         if (const char* e = getenv("TERNASPMM_MAX_WARPS")) max_warps = atoi(e);
-        if (const char* e = getenv("TERNASPMM_PDL")) pdl = atoi(e) != 0;
         if (const char* e = getenv("TERNASPMM_LARGE_MIN_M")) large_min_m = atoi(e) > 0 ? atoi(e) : large_min_m;
         if (const char* e = getenv("TERNASPMM_LARGE_SPLIT")) large_split = atoi(e) != 0;
         if (const char* e = getenv("TERNASPMM_CLUSTER_COST_X10")) cluster_cost_x10 = atoi(e);
@@ -75,12 +76,23 @@ struct Tuning {
         if (const char* e = getenv("TERNASPMM_RPC2")) rpc2 = atoi(e) != 0;
         if (const char* e = getenv("TERNASPMM_FORCE_S")) force_s = atoi(e);
         if (const char* e = getenv("TERNASPMM_FORCE_W")) force_w = atoi(e);
+#endif
     }
 };
 static const Tuning& tuning() {
     static Tuning t;
     return t;
 }
+
+// Shape of the most recent launch made on this thread (test hook, see ternaspmm_last_launch_shape).
+struct LaunchEcho {
+    int kernel = 0, tokens_per_pass = 0, splits = 0, warps = 0, row_tiles_per_cta = 0, ctas = 0;
+};
+static thread_local LaunchEcho t_echo;
+
+// Limit of the device-side waits on a peer (fused tensor-parallel tail), in nanoseconds of the GPU's
+// global timer; changed with ternaspmm_set_wait_limit_ms.
+static unsigned long long g_wait_limit_ns = 1000ull * 1000 * 1000;
 
 struct LaunchShape {
     int splits, warps;
@@ -198,12 +210,19 @@ static cudaError_t launch_small_m(SpmmParams& p, int token_blocks, int warp_slot
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = tuning().pdl ? 2 : 1;
+    t_echo = {MINB == 1 ? 1 : 2, MT * 8, p.splits, warps, shape.rpc, (int)(cfg.gridDim.x * cfg.gridDim.y * cfg.gridDim.z)};
     return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 // 2-D tensor map over the activations x[M][K] (int8): tiles of NT tokens x
 // 128 k, 128-byte swizzle, out-of-range rows and columns read as zero.
+static thread_local int t_inject_encode_failure = 0;   // test hook: the next encode on this thread reports failure
+
 static bool encode_x_map(CUtensorMap* map, const void* x, int M, int K, int NT) {
+    if (t_inject_encode_failure) {
+        t_inject_encode_failure = 0;
+        return false;
+    }
     typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -240,7 +259,7 @@ static cudaError_t launch_large_m(const SpmmParams& p_in, cudaStream_t stream) {
     }
     SpmmParams p = p_in;
     CUtensorMap map;
-    if (!encode_x_map(&map, p.x, p.M, p.K, NT)) return cudaErrorInvalidValue;
+    if (!encode_x_map(&map, p.x, p.M, p.K, NT)) return cudaErrorInvalidValue;   // reported as status 3, nothing is launched
     const long long tiles = (long long)((p.N + 127) / 128) * ((p.M + NT - 1) / NT);
     const int sms = device_sm_count(), KS = (p.K + kLgKStep - 1) / kLgKStep;
     cudaLaunchConfig_t cfg = {};
@@ -282,6 +301,7 @@ static cudaError_t launch_large_m(const SpmmParams& p_in, cudaStream_t stream) {
     attr[0].val.clusterDim.x = p.splits;
     // persistent: one CTA per SM walks over the tiles (with a K split: one tile per cluster)
     cfg.gridDim = dim3(p.splits > 1 ? (unsigned)(tiles * p.splits) : (unsigned)std::min<long long>(tiles, sms), 1, 1);
+    t_echo = {3, NT, p.splits, L::threads / 32, 2, (int)cfg.gridDim.x};
     return cudaLaunchKernelEx(&cfg, kern, p, map);
 }
 
@@ -546,12 +566,12 @@ extern "C" void ternaspmm_tp_finish(float* buf, __nv_bfloat16* ws, float eps, in
     checkLastCudaError(__LINE__);
 }
 
-extern "C" void ternaspmm_tp_allreduce_finish(float** bufs, unsigned int** flags, int rank, int world,
-                                             unsigned int* counters, __nv_bfloat16* ws, float eps, int full_width,
-                                             int M, int N, __nv_bfloat16* residual, __nv_bfloat16* out,
+extern "C" void ternaspmm_tp_allreduce_finish(float** bufs, unsigned int** flags, __nv_bfloat16** outs, int rank,
+                                             int world, unsigned int* counters, __nv_bfloat16* ws, float eps,
+                                             int full_width, int M, int N, __nv_bfloat16* residual,
                                              cudaStream_t stream) {
     t_host_status = ST_OK;
-    if (!bufs || !flags || !counters || !ws || !out || world < 1 || world > 8 || rank < 0 || rank >= world || M < 1 ||
+    if (!bufs || !flags || !outs || !counters || !ws || world < 1 || world > 8 || rank < 0 || rank >= world || M < 1 ||
         N < 4 || (N % 4)) {
         fprintf(stderr, "ternaspmm: tp_allreduce_finish: bad arguments (world 1..8, N a multiple of 4)\n");
         t_host_status = ST_BAD_POINTER;
@@ -559,20 +579,22 @@ extern "C" void ternaspmm_tp_allreduce_finish(float** bufs, unsigned int** flags
     }
     TpPeers peers = {};
     for (int r = 0; r < world; ++r) {
-        if (!bufs[r] || !flags[r]) {
+        if (!bufs[r] || !flags[r] || !outs[r]) {
             t_host_status = ST_BAD_POINTER;
             return;
         }
         peers.buf[r] = bufs[r];
         peers.flag[r] = flags[r];
+        peers.out[r] = outs[r];
     }
     int* status = status_device_ptr();
     if (!status) {
         t_host_status = ST_LAUNCH;
         return;
     }
-    const long long vecs = ((long long)M * N + 3) / 4;
-    int blocks = (int)std::min<long long>((vecs + 255) / 256, 2ll * device_sm_count());
+    // this rank finishes 1/world of the outputs: one 4-element vector per thread, at most two blocks per SM
+    const long long vecs = ((long long)M * N / 4 + world - 1) / world;
+    int blocks = (int)std::max<long long>(1, std::min<long long>((vecs + 255) / 256, 2ll * device_sm_count()));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(blocks, 1, 1);
     cfg.blockDim = dim3(256, 1, 1);
@@ -583,10 +605,26 @@ extern "C" void ternaspmm_tp_allreduce_finish(float** bufs, unsigned int** flags
     cfg.attrs = attr;
     cfg.numAttrs = tuning().pdl ? 1 : 0;
     if (cudaLaunchKernelEx(&cfg, tp_allreduce_finish_kernel, peers, rank, world, counters, counters + 1,
-                           (const __nv_bfloat16*)ws, eps, full_width, M, N, (const __nv_bfloat16*)residual, out,
-                           status) != cudaSuccess)
+                           (const __nv_bfloat16*)ws, eps, full_width, M, N, (const __nv_bfloat16*)residual,
+                           status, g_wait_limit_ns) != cudaSuccess)
         t_host_status = ST_LAUNCH;
     checkLastCudaError(__LINE__);
+}
+
+extern "C" void ternaspmm_debug_inject_host_failure(int kind) {
+    if (kind == 1) t_inject_encode_failure = 1;
+}
+
+extern "C" void ternaspmm_set_wait_limit_ms(int ms) {
+    if (ms < 1) ms = 1;
+    if (ms > 10000) ms = 10000;
+    g_wait_limit_ns = (unsigned long long)ms * 1000ull * 1000ull;
+}
+
+extern "C" void ternaspmm_last_launch_shape(int* out6) {
+    if (!out6) return;
+    out6[0] = t_echo.kernel, out6[1] = t_echo.tokens_per_pass, out6[2] = t_echo.splits, out6[3] = t_echo.warps;
+    out6[4] = t_echo.row_tiles_per_cta, out6[5] = t_echo.ctas;
 }
 
 extern "C" int ternaspmm_last_status(void) {

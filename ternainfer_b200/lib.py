@@ -58,6 +58,12 @@ def load_library() -> ctypes.CDLL:
     lib.gpu_sleep.restype = None
     lib.ternaspmm_last_status.argtypes = []
     lib.ternaspmm_last_status.restype = _I
+    lib.ternaspmm_set_wait_limit_ms.argtypes = [_I]
+    lib.ternaspmm_set_wait_limit_ms.restype = None
+    lib.ternaspmm_last_launch_shape.argtypes = [_P]
+    lib.ternaspmm_last_launch_shape.restype = None
+    lib.ternaspmm_debug_inject_host_failure.argtypes = [_I]
+    lib.ternaspmm_debug_inject_host_failure.restype = None
     lib.ternaspmm_accumulate_i32.argtypes = [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P]
     lib.ternaspmm_accumulate_i32.restype = None
     lib.ternaspmm_linear_segments.argtypes = [_P] * 8 + [_I] * 8 + [_P]
@@ -74,7 +80,7 @@ def load_library() -> ctypes.CDLL:
     lib.ternaspmm_partial_f32.restype = None
     lib.ternaspmm_tp_finish.argtypes = [_P, _P, ctypes.c_float, _I, _I, _I, _P, _P, _P]
     lib.ternaspmm_tp_finish.restype = None
-    lib.ternaspmm_tp_allreduce_finish.argtypes = [_P, _P, _I, _I, _P, _P, ctypes.c_float, _I, _I, _I, _P, _P, _P]
+    lib.ternaspmm_tp_allreduce_finish.argtypes = [_P, _P, _P, _I, _I, _P, _P, ctypes.c_float, _I, _I, _I, _P, _P]
     lib.ternaspmm_tp_allreduce_finish.restype = None
     lib.bitlinear_TernaSpMM_residual.argtypes = [_P] * 8 + [_I] * 4 + [_P, _P]
     lib.bitlinear_TernaSpMM_residual.restype = None
@@ -91,7 +97,8 @@ def load_library() -> ctypes.CDLL:
 EXPORTED_SYMBOLS = (
     "bitlinear_TernaSpMM", "bitlinear_TernaSpMM_decode", "bitlinear_TernaSpMM_prefill",
     "bitlinear_TernaSpMM_benchmark", "checkLastCudaError", "reorder_WT_h", "convert_reorderd",
-    "gpu_sleep", "ternaspmm_last_status", "ternaspmm_accumulate_i32", "ternaspmm_linear_segments", "bitlinear_TernaSpMM_residual", "ternaspmm_quant",
+    "gpu_sleep", "ternaspmm_last_status", "ternaspmm_set_wait_limit_ms", "ternaspmm_last_launch_shape",
+    "ternaspmm_debug_inject_host_failure", "ternaspmm_accumulate_i32", "ternaspmm_linear_segments", "bitlinear_TernaSpMM_residual", "ternaspmm_quant",
     "ternaspmm_scale_quant_sumsq", "ternaspmm_partial_f32", "ternaspmm_tp_finish", "ternaspmm_tp_allreduce_finish", "ternaspmm_rmsnorm_quant", "ternaspmm_relu2_gate_rmsnorm_quant", "ternaspmm_pack_i8",
     "ternaspmm_unpack_i8", "ternaspmm_transcode_reference_layout",
 )

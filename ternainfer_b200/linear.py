@@ -63,10 +63,13 @@ def rmsnorm_quant(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, gated:
 
 
 def TernaInfer_linear(input, compressed_val, TileOffsets_global, TileOffsets_median, bitmap,
-                      workspace, s, ws, ws_num, out_features, mode: str = "auto", residual=None):
+                      workspace, s, ws, ws_num, out_features, mode: str = "auto", residual=None, segments=None):
     """out = TernaSpMM(input_int8, packed weight) as bf16 (model.py:45-92).
     ``input`` is int8 [..., K] on the GPU, ``s`` its per-token bf16 scale,
-    ``ws`` the 4-slot bf16 weight scale with ``ws_num`` non-zero slots."""
+    ``ws`` the 4-slot bf16 weight scale with ``ws_num`` non-zero slots.
+    ``segments`` (optional, not in the reference): lengths of the scale segments;
+    without it the reference's built-in rule decides (equal widths, or
+    2560/640/640 for 3840 outputs)."""
     if not input.is_cuda:
         raise RuntimeError("TernaInfer_linear needs CUDA tensors: the B200 library has no CPU path")
     lib = load_library()
@@ -82,6 +85,14 @@ def TernaInfer_linear(input, compressed_val, TileOffsets_global, TileOffsets_med
     s = s.contiguous()
     ret = torch.empty((M, out_features), dtype=torch.bfloat16, device=input.device)
     stream = torch.cuda.current_stream()
+    if segments is not None and len(segments) > 1 and residual is None:
+        bounds = [sum(segments[:i + 1]) for i in range(len(segments) - 1)] + [2 ** 31 - 1] * 3
+        form = {"auto": -1, "decode": 0, "prefill": 1}[mode]
+        lib.ternaspmm_linear_segments(x2.data_ptr(), bitmap.data_ptr(), TileOffsets_global.data_ptr(),
+                                      TileOffsets_median.data_ptr(), compressed_val.data_ptr(), ret.data_ptr(),
+                                      s.data_ptr(), ws.data_ptr(), ws_num, M, out_features, K, bounds[0], bounds[1],
+                                      bounds[2], form, stream.cuda_stream)
+        return ret.reshape(*out_shape)
     if residual is not None:
         res = residual.reshape(M, out_features)
         assert mode == "auto" and res.is_contiguous() and res.dtype == torch.bfloat16
@@ -127,6 +138,12 @@ class SpBitLinear(nn.Module):
         ws = dic[key + ".weight_scale"]
         self.weight_scale = nn.Parameter(ws.to(dev), requires_grad=False)
         self.ws_num = int((ws != 0).sum().item())
+        # explicit scale-segment lengths when the checkpoint carries them (written by this
+        # library's converter); absent in checkpoints converted by the reference
+        seg = dic.get(key + ".weight_segments")
+        self.segments = [int(v) for v in seg] if seg is not None else None
+        if self.segments is not None:
+            assert sum(self.segments) == out_features and len(self.segments) == self.ws_num
 
     quant_input = staticmethod(quant_input)
 
@@ -135,7 +152,8 @@ class SpBitLinear(nn.Module):
         return TernaInfer_linear(
             input_q,
             self.weight_compressed_val, self.weight_TileOffsets_global, self.weight_TileOffsets_median,
-            self.weight_bitmap, None, s, self.weight_scale, self.ws_num, self.out_features, residual=residual)
+            self.weight_bitmap, None, s, self.weight_scale, self.ws_num, self.out_features, residual=residual,
+            segments=self.segments)
 
     def forward(self, input):
         input, s = quant_input(input)
@@ -145,5 +163,5 @@ class SpBitLinear(nn.Module):
             self.weight_bitmap,
             get_global_workspace(input.device),
             s, self.weight_scale, self.ws_num,
-            self.out_features,
+            self.out_features, segments=self.segments,
         )

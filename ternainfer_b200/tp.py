@@ -21,14 +21,18 @@ cross-rank statistics.  Two modes:
     unsharded layer, numerically within bf16 rounding of it (each rank rounds
     with its own scale).
 ``fused`` - the arithmetic of ``single`` with the collective inside the last
-    kernel: the partials land in a symmetric-memory buffer that every rank has
+    kernel: partials and outputs live in symmetric memory that every rank has
     mapped (``torch.distributed._symmetric_memory``), and
-    ``ternaspmm_tp_allreduce_finish`` signals the peers, waits for them (bounded)
-    and pulls their partials over NVLink with plain loads while it applies the
-    RMS factor and weight scale.  Three launches per linear, no NCCL kernel.
-    Every rank adds the partials in rank order, so all ranks hold identical
-    activations.  Needs ``max_tokens`` at construction (buffer size) and at
-    least two such linears per step (see the kernel's header).
+    ``ternaspmm_tp_allreduce_finish`` is a reduce-scatter plus all-gather in one
+    launch: it signals the peers, waits for them (bounded), reduces this rank's
+    slice of the outputs over all ranks' partials with plain loads over NVLink,
+    applies the RMS factor and weight scale, pushes the finished bf16 slice to
+    every rank and waits for the peers' slices.  Three launches per linear, no
+    NCCL kernel.  Every output element is computed by exactly one rank, so all
+    ranks hold identical activations.  Needs ``max_tokens`` at construction
+    (buffer size).  The returned tensor is a view of the call site's symmetric
+    output buffer: it is overwritten by the next call of the same module.
+    After a step, ``check_status()`` raises if a device-side wait ran out.
 ``exact`` - bit-identical to the unsharded layer: all-reduce the sum of
     squares, normalise, all-reduce (max) the absmax, quantise with the global
     scale, all-reduce the int32 accumulators, then apply the decode epilogue.
@@ -125,12 +129,21 @@ def _quant(x: torch.Tensor, amax: torch.Tensor = None):
     return (x * s).round().clamp(-128, 127).to(torch.int8), s
 
 
-class _PeerBuffers:
-    """One call site's symmetric memory: ``numel`` floats of partials followed by 8 uint32 flags,
-    mapped into every rank of ``group``, plus two local counters.  Construction is collective
-    (every rank must build its modules in the same order)."""
+def check_status():
+    """Raise if the library recorded an error since the last check - in particular status 4: a
+    bounded device-side wait for a peer ran out and the step's outputs were poisoned with NaN.
+    Synchronises the device; call it once per step outside any graph capture."""
+    st = load_library().ternaspmm_last_status()
+    if st != 0:
+        raise RuntimeError(f"TernaSpMM library status {st}" + (" (a wait for a peer rank timed out)" if st == 4 else ""))
 
-    def __init__(self, numel: int, group, device):
+
+class _PeerBuffers:
+    """One call site's symmetric memory: ``numel`` floats of partials, 16 uint32 flags and
+    ``out_numel`` bf16 outputs, mapped into every rank of ``group``, plus two local counters.
+    Construction is collective (every rank must build its modules in the same order)."""
+
+    def __init__(self, numel: int, out_numel: int, group, device):
         import ctypes as C
         import os
         import torch.distributed._symmetric_memory as symm_mem
@@ -138,14 +151,18 @@ class _PeerBuffers:
         grp = group if group is not None else dist.group.WORLD
         self.numel = numel
         self.rank, self.world = dist.get_rank(grp), dist.get_world_size(grp)
-        total = (numel + 3) // 4 * 4 + 8                    # floats, then the flag words
+        nf = (numel + 3) // 4 * 4
+        no = (out_numel + 7) // 8 * 4                       # bf16 outputs, in float units, 16-byte granules
+        total = nf + 16 + no                                # floats, then the flag words, then the outputs
         self.local = symm_mem.empty(total, dtype=torch.float32, device=device)
         self.local.zero_()
         self.handle = symm_mem.rendezvous(self.local, grp)
         ptrs = [int(p) for p in self.handle.buffer_ptrs]
-        flag_off = 4 * ((numel + 3) // 4 * 4)
+        flag_off, out_off = 4 * nf, 4 * (nf + 16)
         self.buf_ptrs = (C.c_void_p * self.world)(*ptrs)
         self.flag_ptrs = (C.c_void_p * self.world)(*[p + flag_off for p in ptrs])
+        self.out_ptrs = (C.c_void_p * self.world)(*[p + out_off for p in ptrs])
+        self.out_local = self.local[nf + 16:].view(torch.bfloat16)
         self.counters = torch.zeros(2, dtype=torch.int32, device=device)
         torch.cuda.synchronize()
         dist.barrier(group=grp)                             # every rank's flags are zero before the first call
@@ -206,7 +223,7 @@ class RowParallelSpBitLinear(nn.Module):
         self._peer = None
         if mode == "fused":
             assert max_tokens > 0, "the fused collective needs max_tokens (size of the symmetric buffer)"
-            self._peer = _PeerBuffers(max_tokens * out_features + max_tokens, group, dev)
+            self._peer = _PeerBuffers(max_tokens * out_features + max_tokens, max_tokens * out_features, group, dev)
 
     def _forward_fused(self, x2: torch.Tensor, residual):
         """GPU path of the ``single`` mode: three launches around one all-reduce."""
@@ -238,7 +255,7 @@ class RowParallelSpBitLinear(nn.Module):
         dev = x2.device
         xq = torch.empty((M, K), dtype=torch.int8, device=dev)
         s = torch.empty((M,), dtype=torch.bfloat16, device=dev)
-        out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        out = pb.out_local[:M * N].view(M, N)              # every rank's kernel writes its slice here
         cv, tg, tm, bm = self.packed
         st = _stream()
         base = pb.local.data_ptr()
@@ -246,9 +263,9 @@ class RowParallelSpBitLinear(nn.Module):
                                         xq.data_ptr(), s.data_ptr(), base + 4 * M * N, st)
         lib.ternaspmm_partial_f32(xq.data_ptr(), bm.data_ptr(), tg.data_ptr(), tm.data_ptr(), cv.data_ptr(),
                                   base, s.data_ptr(), M, N, K, st)
-        lib.ternaspmm_tp_allreduce_finish(pb.buf_ptrs, pb.flag_ptrs, pb.rank, pb.world, pb.counters.data_ptr(),
-                                          self.ws_bf16.data_ptr(), self.eps, K * self.tp, M, N,
-                                          residual.data_ptr() if residual is not None else None, out.data_ptr(), st)
+        lib.ternaspmm_tp_allreduce_finish(pb.buf_ptrs, pb.flag_ptrs, pb.out_ptrs, pb.rank, pb.world,
+                                          pb.counters.data_ptr(), self.ws_bf16.data_ptr(), self.eps, K * self.tp, M, N,
+                                          residual.data_ptr() if residual is not None else None, st)
         return out
 
     def forward(self, x, residual=None):

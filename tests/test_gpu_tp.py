@@ -125,31 +125,137 @@ def test_two_emulated_k_shards_against_unsharded_layer(lib):
     assert (err.pow(2).mean().sqrt() / want.pow(2).mean().sqrt()).item() < 0.02
 
 
+def _finish_inputs(M, N, W, world, seed=3):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    bufs = []
+    for _ in range(world):
+        b = torch.randn(M * N + M, generator=g, device="cuda")
+        b[M * N:] = b[M * N:].abs() * W / world
+        bufs.append(b)
+    ws = torch.tensor([0.03]).to(torch.bfloat16).cuda()
+    res = torch.randn((M, N), generator=g, device="cuda").to(torch.bfloat16)
+    total = torch.stack(bufs).sum(0) if world != 2 else bufs[0] + bufs[1]
+    want = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    from ternainfer_b200 import load_library
+    load_library().ternaspmm_tp_finish(total.data_ptr(), ws.data_ptr(), 1e-5, W, M, N, res.data_ptr(),
+                                       want.data_ptr(), st)
+    torch.cuda.synchronize()
+    return bufs, ws, res, want, st
+
+
+def _ptrs(tensors):
+    import ctypes as C
+    return (C.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+
+
 def test_allreduce_finish_kernel_with_one_rank(lib):
     """World size 1: the fused tail degenerates to the plain finish kernel (no peer to wait for);
     two calls in a row exercise the run counter."""
-    import ctypes as C
     M, N, W = 24, 1024, 4096
-    g = torch.Generator(device="cuda").manual_seed(3)
-    buf = torch.randn(M * N + M, generator=g, device="cuda")
-    buf[M * N:] = buf[M * N:].abs() * W
-    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    bufs, ws, res, want, st = _finish_inputs(M, N, W, 1)
+    flags = torch.zeros(16, dtype=torch.int32, device="cuda")
     counters = torch.zeros(2, dtype=torch.int32, device="cuda")
-    ws = torch.tensor([0.03]).to(torch.bfloat16).cuda()
-    res = torch.randn((M, N), generator=g, device="cuda").to(torch.bfloat16)
-    want = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
     got = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
-    st = torch.cuda.current_stream().cuda_stream
-    lib.ternaspmm_tp_finish(buf.data_ptr(), ws.data_ptr(), 1e-5, W, M, N, res.data_ptr(), want.data_ptr(), st)
-    bufs, flg = (C.c_void_p * 1)(buf.data_ptr()), (C.c_void_p * 1)(flags.data_ptr())
     for call in range(2):
         got.zero_()
-        lib.ternaspmm_tp_allreduce_finish(bufs, flg, 0, 1, counters.data_ptr(), ws.data_ptr(), 1e-5, W, M, N,
-                                          res.data_ptr(), got.data_ptr(), st)
+        lib.ternaspmm_tp_allreduce_finish(_ptrs(bufs), _ptrs([flags]), _ptrs([got]), 0, 1, counters.data_ptr(),
+                                          ws.data_ptr(), 1e-5, W, M, N, res.data_ptr(), st)
         torch.cuda.synchronize()
         assert lib.ternaspmm_last_status() == 0
         assert torch.equal(got, want)
         assert counters.tolist() == [call + 1, 0]
+
+
+@pytest.mark.parametrize("M,N", [(24, 1024), (64, 8192), (1, 64), (5, 2564)])
+def test_reduce_scatter_all_gather_tail_two_emulated_ranks(lib, M, N):
+    """Both ranks' buffers live on this GPU.  A rank's launch never waits for another launch: the
+    peer's signals are raised by the host beforehand, so the two launches run one after the other.
+    Each launch reduces its own slice and pushes it into both outputs; after both, each output holds
+    the complete result, equal to the plain finish kernel on the summed partials."""
+    W = 4096
+    bufs, ws, res, want, st = _finish_inputs(M, N, W, 2, seed=M + N)
+    flags = [torch.zeros(16, dtype=torch.int32, device="cuda") for _ in range(2)]
+    counters = [torch.zeros(2, dtype=torch.int32, device="cuda") for _ in range(2)]
+    outs = [torch.zeros((M, N), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    for call in range(1, 3):
+        for o_ in outs:
+            o_.zero_()
+        for r in range(2):
+            peer = 1 - r
+            # what the peer's launch would do: "partials ready" and "slice pushed" for this call
+            flags[r][peer] = call
+            flags[r][8 + peer] = call
+        torch.cuda.synchronize()
+        for r in range(2):
+            lib.ternaspmm_tp_allreduce_finish(_ptrs(bufs), _ptrs(flags), _ptrs(outs), r, 2, counters[r].data_ptr(),
+                                              ws.data_ptr(), 1e-5, W, M, N, res.data_ptr(), st)
+            torch.cuda.synchronize()
+            assert lib.ternaspmm_last_status() == 0
+        assert torch.equal(outs[0], want) and torch.equal(outs[1], want)
+        assert counters[0].tolist() == [call, 0] and counters[1].tolist() == [call, 0]
+        # each launch signalled its peer twice on top of the host's values
+        assert flags[1][0].item() >= call and flags[0][1].item() >= call
+
+
+def test_peer_wait_runs_out_with_status_4_and_poisoned_output(lib):
+    """A peer that never signals: the bounded wait (5 ms here) runs out, the kernel returns on its
+    own with status 4 and an output full of NaN, and the context stays usable: the next call, with
+    the peer's signals present, succeeds."""
+    M, N, W = 8, 512, 4096
+    bufs, ws, res, want, st = _finish_inputs(M, N, W, 2, seed=77)
+    flags = [torch.zeros(16, dtype=torch.int32, device="cuda") for _ in range(2)]
+    counters = torch.zeros(2, dtype=torch.int32, device="cuda")
+    outs = [torch.zeros((M, N), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    lib.ternaspmm_set_wait_limit_ms(5)
+    try:
+        lib.ternaspmm_tp_allreduce_finish(_ptrs(bufs), _ptrs(flags), _ptrs(outs), 0, 2, counters.data_ptr(),
+                                          ws.data_ptr(), 1e-5, W, M, N, res.data_ptr(), st)
+        torch.cuda.synchronize()
+        assert lib.ternaspmm_last_status() == 4
+        assert torch.isnan(outs[0].float()).all()
+        assert (outs[1] == 0).all()                      # nothing was pushed to the peer
+        assert counters.tolist() == [1, 0]               # the call is closed; the next one is number 2
+        flags[0][1] = 2
+        flags[0][9] = 2
+        torch.cuda.synchronize()
+        lib.ternaspmm_tp_allreduce_finish(_ptrs(bufs), _ptrs(flags), _ptrs(outs), 0, 2, counters.data_ptr(),
+                                          ws.data_ptr(), 1e-5, W, M, N, res.data_ptr(), st)
+        torch.cuda.synchronize()
+        assert lib.ternaspmm_last_status() == 0
+        half = M * N // 2
+        assert torch.equal(outs[0].reshape(-1)[:half], want.reshape(-1)[:half])   # rank 0's slice, in both outputs
+        assert torch.equal(outs[1].reshape(-1)[:half], want.reshape(-1)[:half])
+    finally:
+        lib.ternaspmm_set_wait_limit_ms(1000)
+
+
+def test_tensor_map_encode_failure_is_status_3_without_a_launch(lib):
+    """Host-side fault injection: the tensor-map encode of the tcgen05 kernel's launcher reports
+    failure; the call must end with status 3, launch nothing and leave the output untouched."""
+    from gpu_util import Packed, dev
+    import ternaspmm_oracle as o
+    M, N, K = 128, 256, 256
+    w = o.make_ternary(N, K, 0.45, 5)
+    xq, s = o.make_activations(M, K, 6)
+    pk = Packed(w)
+    x_d, s_d = dev(xq), dev(o.f32_to_bf16_bits(s.reshape(-1)))
+    ws_d = dev(o.f32_to_bf16_bits(o.make_ws(1)))
+    out = torch.full((M * N,), 0x7B7B, dtype=torch.int16, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+
+    def run():
+        lib.bitlinear_TernaSpMM(x_d.data_ptr(), pk.bm.data_ptr(), pk.tg.data_ptr(), pk.tm.data_ptr(), pk.cv.data_ptr(),
+                                out.data_ptr(), s_d.data_ptr(), ws_d.data_ptr(), 1, M, N, K, 7, 0, st)
+        torch.cuda.synchronize()
+
+    lib.ternaspmm_debug_inject_host_failure(1)
+    run()
+    assert lib.ternaspmm_last_status() == 3
+    assert (out == 0x7B7B).all()
+    run()                                                # the injection is one-shot
+    assert lib.ternaspmm_last_status() == 0
+    assert not (out == 0x7B7B).all()
 
 
 def _two_rank_worker(rank, world, port, ok):
@@ -180,7 +286,11 @@ def _two_rank_worker(rank, world, port, ok):
     for _ in range(3):
         yb, yc = b(xs, residual=res), c(xs, residual=res)
         good = good and torch.equal(ya, yb) and torch.equal(yb, yc)
+    # the same call site twice in a row: its buffers may be reused at once
+    for _ in range(4):
+        good = good and torch.equal(b(xs, residual=res), ya)
     torch.cuda.synchronize()
+    tp.check_status()
     ok[rank] = int(good and load_ok())
     dist.barrier()
     torch.cuda.synchronize()
@@ -199,7 +309,11 @@ def test_fused_collective_matches_nccl_on_two_gpus(lib):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     ok = ctx.Array("i", [0, 0])
-    procs = [ctx.Process(target=_two_rank_worker, args=(r, 2, 29577, ok)) for r in range(2)]
+    import socket
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
+    procs = [ctx.Process(target=_two_rank_worker, args=(r, 2, port, ok)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:

@@ -105,6 +105,50 @@ def test_two_rank_tensor_parallel_linears(mode):
         assert res["row_max_rel"] < 0.05, res   # one collective: max error under 5 % of the output RMS (quantisation noise)
 
 
+def _leaving_worker(rank, world, port, q):
+    """Rank 1 leaves between two steps (no collective in flight); rank 0 must find out through an
+    error from its next collective within the process group's timeout, not hang."""
+    import datetime
+    import time
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=10))
+    from ternainfer_b200 import tp
+    tp._accumulate_i32, tp._linear_segments = _oracle_accumulate, _oracle_linear_segments
+    torch.manual_seed(0)
+    dim, ffn, M = 128, 256, 3
+    w2 = torch.from_numpy(o.make_ternary(dim, ffn, 0.45, 2))
+    dic = {}
+    tp.shard_checkpoint_entry(dic, "w2", w2, torch.tensor([0.025, 0, 0, 0]).to(torch.bfloat16), None, "row", rank, world)
+    row = tp.RowParallelSpBitLinear(ffn // world, dim, dic, "w2", None, torch.ones(ffn // world), 1e-5, "single")
+    x = torch.randn(M, ffn // world).to(torch.bfloat16)
+    y = row(x)                       # step 1: both ranks take part
+    dist.barrier()
+    if rank == 1:
+        os._exit(0)                  # leaves between steps
+    t0 = time.monotonic()
+    try:
+        row(x)                       # step 2: the peer is gone
+        q.put(("no error", time.monotonic() - t0, bool(torch.isfinite(y.float()).all())))
+    except Exception as e:           # gloo reports the closed connection or the timeout
+        q.put((type(e).__name__, time.monotonic() - t0, bool(torch.isfinite(y.float()).all())))
+    os._exit(0)
+
+
+def test_rank_leaving_between_steps_raises_on_the_other_rank():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_leaving_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    kind, seconds, step1_ok = q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+    assert step1_ok
+    assert kind != "no error", "the surviving rank's collective returned although its peer had left"
+    assert seconds < 60
+
+
 def test_shard_helpers():
     from ternainfer_b200 import tp
     w = torch.arange(12 * 128).reshape(12, 128)
