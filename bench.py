@@ -1,9 +1,9 @@
 #!/usr/bin/env python
 """Benchmark of the TernaSpMM hot path on B200.
 
-Workload (BASELINE.json configs[1], the linear-layer sweep): the four ternary
-linears of a BitNet-b1.58-2B decoder layer - QKV 2560->3840 (3 scale segments),
-O 2560->2560, gate-up 2560->13824 (2 segments), down 6912->2560 - for
+Headline workload (the linear-layer sweep): the four ternary linears of a
+BitNet-b1.58-2B decoder layer - QKV 2560->3840 (3 scale segments), O
+2560->2560, gate-up 2560->13824 (2 segments), down 6912->2560 - for
 ``--layers`` layers with distinct random weights (30 layers = 410 MB of
 compressed weights, more than three times the L2, so every call streams its
 weights from HBM) at ``--tokens`` tokens.  One step = one pass over all
@@ -15,6 +15,14 @@ activations + scales + bf16 outputs) of all ranks per second with every input
 resident in HBM, the step replayed as a CUDA graph; ``e2e`` = the same metric
 through the Python call site (``TernaInfer_linear``) with the activations
 copied from pinned host memory and the outputs copied back every step.
+On one GPU the line also carries ``by_tokens`` (the same sweep at 1 and 16
+tokens), ``ref_kernels_b200`` (the reference's own small-batch CUDA kernels,
+built for sm_100a from the reference checkout, timed in the same loop at 8, 16
+and 64 tokens next to this library) and ``decode`` (greedy decode tokens/s of
+the 30-layer model at batch 1 and 8).  On N > 1 GPUs the sweep runs as
+independent replicas (the 2B model's 5 KV heads do not shard) and the line
+carries ``tp``: the sharded linear stack of the 8192-wide model with one
+collective per row-parallel linear, NCCL and fused.
 ``--impl reference`` times the CPU restatement of the reference's arithmetic
 (the reference has no CPU implementation of this path and its CUDA library
 does not build without an un-vendored CUTLASS) on the host cores.
@@ -109,10 +117,24 @@ class ClockSampler:
 # only as the thing to compare against, never on the GPU arm's path).
 # ----------------------------------------------------------------------------
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of spmm_small_m_kernel from one ncu capture of the
-# four layer shapes at full size (profiles/spmm_small_m_bitnet2b_sweep_M8.md: 1.990 + 1.346 + 7.017 + 3.572 MB),
-# averaged like the step's launches (each shape once per layer); token count -> bytes.
-NCU_DRAM_BYTES_PER_LAUNCH = {8: (1.990e6 + 1.346e6 + 7.017e6 + 3.572e6) / 4}
+def ncu_traffic(kernel, tokens):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of ``kernel`` at ``tokens`` tokens,
+    averaged over the step's launches, from the table that is written next to the ncu summaries
+    when a capture is processed (profiles/ncu_traffic.json); None when there is no entry."""
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    try:
+        return float(json.load(open(path))[kernel][str(tokens)])
+    except Exception:
+        return None
+
+
+def sweep_config(args, world):
+    """The workload description both arms print (the driver compares them)."""
+    return {"workload": f"bitnet2b_linear_sweep_M{args.tokens}", "tokens": args.tokens, "layers": args.layers,
+            "linears_per_step": 4 * args.layers, "p_zero": P_ZERO, "seed": args.seed,
+            "l2_policy": "inputs larger than L2: each step streams the distinct compressed weights of all layers "
+                         "(410 MB at 30 layers)",
+            "parallelism": "replicas only" if world > 1 else "single GPU"}
 
 
 def cpu_sample(tokens, seconds_budget, seed=1234):
@@ -120,6 +142,7 @@ def cpu_sample(tokens, seconds_budget, seed=1234):
     import ternaspmm_oracle as o
     import c_oracle
     lib = c_oracle.load()
+    lib.oracle_set_num_threads(os.cpu_count() or 1)    # launchers export OMP_NUM_THREADS=1; use the host's cores
     cores = int(lib.oracle_num_threads())
     items, alg = [], 0
     for li, (name, N, K, ws_num) in enumerate(SHAPES):
@@ -146,9 +169,11 @@ def cpu_sample(tokens, seconds_budget, seed=1234):
 
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
-    # a step = a bounded sample of the sweep (some passes over one layer); the whole run stays near a minute
+    # a step = a bounded sample of the sweep (some passes over one layer); the whole run stays near a minute.
+    # The value is what ALL host cores of the box deliver, whatever N is: there is one host.
     one_pass, alg, cores, reps, _ = cpu_sample(args.tokens, max(0.1, 60.0 / max(1, args.steps)))
     for _ in range(args.warmup):
         one_pass()
@@ -158,14 +183,13 @@ def run_reference_arm(args):
             one_pass()
     dt = time.perf_counter() - t0
     val = alg * reps * args.steps / dt / 1e9
-    sample = f"{reps} passes over one layer (4 linears) per step at {args.tokens} tokens, dense ternary int8 weights"
+    sample = (f"{reps} passes over one layer (4 linears) per step at {args.tokens} tokens, dense ternary int8 weights; "
+              "CPU restatement of the reference arithmetic (C, OpenMP) - the reference has no CPU path")
     line = {
         "impl": "reference", "metric": "ternaspmm_algorithmic_GBps", "value": val, "unit": "GB/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8xternary->int32->bf16",
-        "data": "synthetic",
-        "config": {"workload": f"bitnet2b_linear_sweep_M{args.tokens}", "tokens": args.tokens, "p_zero": P_ZERO,
-                   "note": "CPU restatement of the reference arithmetic (C, OpenMP); the reference has no CPU path"},
+        "data": "synthetic", "config": sweep_config(args, world),
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -177,7 +201,8 @@ def run_reference_arm(args):
 # GPU arm
 # ----------------------------------------------------------------------------
 
-def build_workload(torch, layers, tokens, seed, device):
+def build_workload(torch, layers, seed, device):
+    """The packed weights of `layers` layers (distinct seeded random ternary matrices)."""
     from ternainfer_b200.convert import compress_weight, compressed_nbytes
     gen = torch.Generator(device=device)
     work, wbytes_total = [], 0
@@ -192,7 +217,7 @@ def build_workload(torch, layers, tokens, seed, device):
             ws = torch.zeros(4, device=device)
             ws[:ws_num] = torch.rand(ws_num, generator=gen, device=device) * 0.04 + 0.01
             item = dict(name=name, N=N, K=K, ws_num=ws_num, cv=cv, tg=tg, tm=tm, bm=bm, ws=ws.to(torch.bfloat16),
-                        wbytes=nbytes, alg=nbytes + tokens * K + 2 * tokens + 8 + 2 * tokens * N)
+                        wbytes=nbytes)
             if layer == 0:
                 item["dense"] = w.cpu().numpy()
             work.append(item)
@@ -201,38 +226,105 @@ def build_workload(torch, layers, tokens, seed, device):
     return work, wbytes_total
 
 
-def run_gpu_arm(args):
-    import torch
-    import torch.distributed as dist
-    from ternainfer_b200 import load_library
-    from ternainfer_b200.linear import TernaInfer_linear, quant_input
+def algorithmic_bytes(it, tokens):
+    """Compressed weight + int8 activations + per-token scales + weight scales + bf16 outputs of one call."""
+    return it["wbytes"] + tokens * it["K"] + 2 * tokens + 8 + 2 * tokens * it["N"]
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA GPU: the TernaSpMM library has no CPU path")
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-    lib = load_library()   # raises if the CUDA library is missing
-    M = args.tokens
 
-    work, wbytes_total = build_workload(torch, args.layers, M, args.seed + 7919 * rank, device)
-    alg_step = sum(it["alg"] for it in work)
+class Env:
+    """Process-wide state of a GPU run."""
 
-    # activations: one bf16 matrix per input width, quantised once (resident leg)
-    gen = torch.Generator(device="cpu").manual_seed(args.seed + 5)
+    def __init__(self):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist = torch, dist
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA GPU: the TernaSpMM library has no CPU path")
+        torch.cuda.set_device(self.local_rank)
+        self.device = torch.device("cuda", self.local_rank)
+        if self.world > 1:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # peer memory by plain loads/stores only
+            dist.init_process_group("nccl", device_id=self.device)
+        from ternainfer_b200 import load_library
+        self.lib = load_library()   # raises if the CUDA library is missing
+        self.stream = torch.cuda.Stream(device=self.device)
+
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+            self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, ms):
+        t = self.torch.tensor([ms], dtype=self.torch.float64, device=self.device)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def time_replays(self, replay, steps, warmup, min_load_s=0.0):
+        """`warmup` untimed replays (plus, with min_load_s, enough further ones to keep the GPU under
+        this load for that long, so that the clock sampler sees it), then EXACTLY `steps` timed ones
+        between CUDA events on the launching stream, barrier + synchronize on both sides; max over ranks."""
+        torch = self.torch
+        with torch.cuda.stream(self.stream):
+            for _ in range(warmup):
+                replay()
+            if min_load_s > 0:
+                self.stream.synchronize()
+                t0 = time.perf_counter()
+                replay()
+                self.stream.synchronize()
+                one = max(time.perf_counter() - t0, 1e-6)
+                for _ in range(min(20000, int(min_load_s / one))):
+                    replay()
+            self.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(self.stream)
+            for _ in range(steps):
+                replay()
+            e1.record(self.stream)
+            self.barrier()
+        return self.max_over_ranks(e0.elapsed_time(e1))
+
+
+def quantised_inputs(env, M, seed):
+    torch = env.torch
+    from ternainfer_b200.linear import quant_input
+    gen = torch.Generator(device="cpu").manual_seed(seed + 5)
     x_host = {K: torch.randn((M, K), generator=gen).to(torch.bfloat16).pin_memory() for K in (2560, 6912)}
     xq, s = {}, {}
     for K, xh in x_host.items():
-        xq[K], s[K] = quant_input(xh.to(device))
+        xq[K], s[K] = quant_input(xh.to(env.device))
         s[K] = s[K].contiguous()
-    xq_host = {K: v.cpu().pin_memory() for K, v in xq.items()}
-    s_host = {K: v.cpu().pin_memory() for K, v in s.items()}
-    outs = [torch.empty((M, it["N"]), dtype=torch.bfloat16, device=device) for it in work]
-    stream = torch.cuda.Stream(device=device)
+    return xq, s
+
+
+def check_layer0_against_oracle(env, work, outs, xq, s):
+    """Sanity check outside the timed region: the first layer's outputs against the CPU oracle."""
+    torch = env.torch
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import ternaspmm_oracle as o
+    for it, out in zip(work[:len(SHAPES)], outs[:len(SHAPES)]):
+        K = it["K"]
+        want = o.ternaspmm(xq[K].cpu().numpy(), it["dense"], s[K].float().cpu().numpy().reshape(-1),
+                           it["ws"].float().cpu().numpy(), it["ws_num"])
+        got = out.view(torch.int16).cpu().numpy().view(np.uint16)
+        if not (got == want).all():
+            raise SystemExit(f"bench sanity check failed for {it['name']}: GPU result differs from the oracle")
+    if env.lib.ternaspmm_last_status() != 0:
+        raise SystemExit("bench: library reported a non-zero status")
+
+
+def sweep_leg(env, work, M, args, headline):
+    """One pass over all linears at M tokens per step, inputs resident in HBM, the step replayed as one
+    CUDA graph.  Returns value / ms_per_step / roofline for that token count."""
+    torch, lib = env.torch, env.lib
+    xq, s = quantised_inputs(env, M, args.seed)
+    outs = [torch.empty((M, it["N"]), dtype=torch.bfloat16, device=env.device) for it in work]
+    alg_step = sum(algorithmic_bytes(it, M) for it in work)
 
     def launch_all():
         st = torch.cuda.current_stream().cuda_stream
@@ -242,71 +334,50 @@ def run_gpu_arm(args):
                                     it["cv"].data_ptr(), out.data_ptr(), s[K].data_ptr(), it["ws"].data_ptr(),
                                     it["ws_num"], M, it["N"], K, 7, 0, st)
 
-    # sanity (outside the timed region): layer 0 against the CPU oracle
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
-    import ternaspmm_oracle as o
-    with torch.cuda.stream(stream):
+    with torch.cuda.stream(env.stream):
         launch_all()
-    stream.synchronize()
-    for it, out in zip(work[:len(SHAPES)], outs[:len(SHAPES)]):
-        K = it["K"]
-        want = o.ternaspmm(xq[K].cpu().numpy(), it["dense"], s[K].float().cpu().numpy().reshape(-1),
-                           it["ws"].float().cpu().numpy(), it["ws_num"])
-        got = out.view(torch.int16).cpu().numpy().view(np.uint16)
-        if not (got == want).all():
-            raise SystemExit(f"bench sanity check failed for {it['name']}: GPU result differs from the oracle")
-    if lib.ternaspmm_last_status() != 0:
-        raise SystemExit("bench: library reported a non-zero status")
-
-    # resident leg: the whole step as one CUDA graph
+    env.stream.synchronize()
+    check_layer0_against_oracle(env, work, outs, xq, s)
     graph = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(stream):
-        with torch.cuda.graph(graph, stream=stream):
+    with torch.cuda.stream(env.stream):
+        with torch.cuda.graph(graph, stream=env.stream):
             launch_all()
+    ms = env.time_replays(graph.replay, args.steps, args.warmup, min_load_s=1.0 if headline else 0.2)
+    peak, peak_kind = measured_peak()
+    launches = len(work)
+    per_launch_us = ms * 1e3 / (args.steps * launches)
+    achieved = (alg_step / launches) / (per_launch_us * 1e-6) / 1e9
+    res = {"value": alg_step * env.world * args.steps / (ms * 1e-3) / 1e9, "unit": "GB/s",
+           "ms_per_step": ms / args.steps,
+           "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                        "peak_kind": "of " + peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
+                        "kernel": "spmm_small_m_kernel", "avg_launch_us": per_launch_us,
+                        "algorithmic_bytes_per_launch": alg_step / launches,
+                        "traffic": ncu_traffic("spmm_small_m_kernel", M)},
+           "gpu_launches": launches * args.steps}
+    return res, (xq, s, alg_step)
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
 
-    sampler = ClockSampler(local_rank)
-    with torch.cuda.stream(stream):
-        for _ in range(args.warmup):
-            graph.replay()
-        barrier()
-        if rank == 0:
-            sampler.start()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev0.record(stream)
-        for _ in range(args.steps):
-            graph.replay()
-        ev1.record(stream)
-        barrier()
-    ms = ev0.elapsed_time(ev1)
-    t = torch.tensor([ms], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max = float(t.item())
-
-    # end-to-end leg: Python call site, host buffers in and out every step
+def e2e_leg(env, work, M, args, xq, s, alg_step):
+    """The same step through the Python call site with HOST buffers: this step's activations come from
+    pinned host memory, every output goes back to pinned host memory (on a side stream that forks after
+    its producer, so the copies overlap the following linears).  Captured once, exactly as the reference's
+    generate.py captures its forward; a step is one replay."""
+    torch = env.torch
+    from ternainfer_b200.linear import TernaInfer_linear
+    xq_host = {K: v.cpu().pin_memory() for K, v in xq.items()}
+    s_host = {K: v.cpu().pin_memory() for K, v in s.items()}
     out_host = [torch.empty((M, it["N"]), dtype=torch.bfloat16).pin_memory() for it in work]
-    xq_dev = {K: torch.empty_like(v, device=device) for K, v in xq_host.items()}
-    s_dev = {K: torch.empty_like(v, device=device) for K, v in s_host.items()}
+    xq_dev = {K: torch.empty_like(v, device=env.device) for K, v in xq_host.items()}
+    s_dev = {K: torch.empty_like(v, device=env.device) for K, v in s_host.items()}
     h2d = sum(v.numel() * v.element_size() for v in xq_host.values()) + \
         sum(v.numel() * v.element_size() for v in s_host.values())
     d2h = sum(v.numel() * v.element_size() for v in out_host)
-
-    # The calls go through the Python call site (TernaInfer_linear) once, under CUDA-graph capture,
-    # exactly as the reference's generate.py captures its forward.  The copies are part of the
-    # captured step: this step's activations come from pinned host memory on the main stream, and
-    # every output goes back to pinned host memory on a side stream that forks after its producer,
-    # so the device-to-host copies overlap the following linears.  A step is one replay.
-    e2e_outs = []
-    e2e_graph = torch.cuda.CUDAGraph()
-    side = torch.cuda.Stream(device=device)
-    with torch.cuda.stream(stream):
-        with torch.cuda.graph(e2e_graph, stream=stream):
+    keep = []
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(device=env.device)
+    with torch.cuda.stream(env.stream):
+        with torch.cuda.graph(graph, stream=env.stream):
             for K in xq_host:
                 xq_dev[K].copy_(xq_host[K], non_blocking=True)
                 s_dev[K].copy_(s_host[K], non_blocking=True)
@@ -314,44 +385,132 @@ def run_gpu_arm(args):
                 K = it["K"]
                 y = TernaInfer_linear(xq_dev[K], it["cv"], it["tg"], it["tm"], it["bm"], None, s_dev[K],
                                       it["ws"], it["ws_num"], it["N"])
-                e2e_outs.append(y)
+                keep.append(y)
                 done = torch.cuda.Event()
-                done.record(stream)
+                done.record(env.stream)
                 side.wait_event(done)
                 with torch.cuda.stream(side):
                     oh.copy_(y, non_blocking=True)
             joined = torch.cuda.Event()
             joined.record(side)
-            stream.wait_event(joined)
+            env.stream.wait_event(joined)
+    ms = env.time_replays(graph.replay, args.steps, max(3, args.warmup))
+    return {"value": alg_step * env.world * args.steps / (ms * 1e-3) / 1e9, "unit": "GB/s",
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms / args.steps,
+            "api": "ternainfer_b200.linear.TernaInfer_linear captured in a CUDA graph together with its H2D and "
+                   "(side-stream) D2H copies; one replay per step"}
 
-    def e2e_step():
-        e2e_graph.replay()
 
-    with torch.cuda.stream(stream):
-        for _ in range(max(3, args.warmup)):
-            e2e_step()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(args.steps):
-            e2e_step()
-        e1.record(stream)
-        barrier()
-    clocks = sampler.stop() if rank == 0 else None
-    t2 = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t2.item())
+def ref_kernels_leg(env, work, args):
+    """The reference's own small-batch CUDA kernels (SpMM + split-K reduction, SPLIT_K = 7 as model.py
+    passes it), compiled for sm_100a from the reference checkout into oracle/_ref, next to this library
+    in the same loop: one pass over `layers` x 4 linears per step, every call on its own copy of the
+    packed weights so that all of them stream from HBM.  The reference supports 8, 16, 32 and 64 tokens."""
+    torch = env.torch
+    so = os.path.join(ROOT, "oracle", "_ref", "libternaspmm_ref_decode.so")
+    if not os.path.exists(so):
+        return {"unavailable": "oracle/_ref/libternaspmm_ref_decode.so not built (needs the reference checkout)"}
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import ternaspmm_oracle as o
+    ref = ctypes.CDLL(so)
+    P, I = ctypes.c_void_p, ctypes.c_int
+    ref.ref_bitlinear_TernaSpMM_decode.argtypes = [P] * 8 + [I] * 5 + [P, P]
+    ref.ref_bitlinear_TernaSpMM_decode.restype = I
 
-    if rank == 0:
-        peak, peak_kind = measured_peak()
-        launches = len(work)
-        value = alg_step * world * args.steps / (ms_max * 1e-3) / 1e9
-        per_launch_us = ms_max * 1e3 / (args.steps * launches)
-        achieved = (alg_step / launches) / (per_launch_us * 1e-6) / 1e9
-        e2e_val = alg_step * world * args.steps / (e2e_ms * 1e-3) / 1e9
+    def dev(a):
+        return torch.from_numpy(np.ascontiguousarray(a).view(np.uint8).reshape(-1).copy()).to(env.device)
+
+    layers = len(work) // len(SHAPES)
+    packed = []   # per shape: `layers` device copies of the reference-layout arrays of layer 0's weight
+    for it in work[:len(SHAPES)]:
+        cv, tg, tm, bm = o.compress_weight_ref(it["dense"])
+        cv = np.concatenate([cv, np.zeros(16, np.uint32)])        # the reference kernels prefetch past the ends
+        tg = np.concatenate([tg, np.full(8, tg[-1], np.int32)])
+        tm = np.concatenate([tm, np.zeros(16, np.uint16)])
+        base = [dev(a) for a in (bm, tg, tm, cv)]
+        packed.append([base] + [[t.clone() for t in base] for _ in range(layers - 1)])
+    out = {"split_k": 7, "layers": layers, "note": "same weights, activations and scales on both sides; ours = "
+           "bitlinear_TernaSpMM of this library; reference = mySpMM_Kernel_bitmap_v3 + SplitK_Reduction"}
+    for M in (8, 16, 64):
+        xq, s = quantised_inputs(env, M, args.seed)
+        outs = [torch.empty((M, it["N"]), dtype=torch.bfloat16, device=env.device) for it in work[:len(SHAPES)]]
+        wsp = torch.zeros(7 * M * 13824, dtype=torch.int32, device=env.device)
+
+        def launch_ref():
+            st = torch.cuda.current_stream().cuda_stream
+            for layer in range(layers):
+                for si, it in enumerate(work[:len(SHAPES)]):
+                    bm, tg, tm, cv = packed[si][layer]
+                    K = it["K"]
+                    rc = ref.ref_bitlinear_TernaSpMM_decode(xq[K].data_ptr(), bm.data_ptr(), tg.data_ptr(), tm.data_ptr(),
+                                                            cv.data_ptr(), outs[si].data_ptr(), s[K].data_ptr(),
+                                                            it["ws"].data_ptr(), it["ws_num"], M, it["N"], K, 7,
+                                                            wsp.data_ptr(), st)
+                    if rc != 0:
+                        raise SystemExit(f"reference kernels: CUDA error {rc}")
+
+        ours_outs = [torch.empty((M, it["N"]), dtype=torch.bfloat16, device=env.device) for it in work]
+
+        def launch_ours():
+            st = torch.cuda.current_stream().cuda_stream
+            for it, o_ in zip(work, ours_outs):
+                K = it["K"]
+                env.lib.bitlinear_TernaSpMM(xq[K].data_ptr(), it["bm"].data_ptr(), it["tg"].data_ptr(),
+                                            it["tm"].data_ptr(), it["cv"].data_ptr(), o_.data_ptr(), s[K].data_ptr(),
+                                            it["ws"].data_ptr(), it["ws_num"], M, it["N"], K, 7, 0, st)
+
+        res = {}
+        for name, fn in (("reference", launch_ref), ("ours", launch_ours)):
+            with torch.cuda.stream(env.stream):
+                fn()
+            env.stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(env.stream):
+                with torch.cuda.graph(g, stream=env.stream):
+                    fn()
+            ms = env.time_replays(g.replay, args.steps, args.warmup)
+            res[name + "_ms_per_step"] = ms / args.steps
+        # layer 0: both sides must agree bit for bit
+        same = all(torch.equal(a, b) for a, b in zip(outs, ours_outs[:len(SHAPES)]))
+        alg = sum(algorithmic_bytes(it, M) for it in work)
+        res.update({"reference_GBps": alg / (res["reference_ms_per_step"] * 1e-3) / 1e9,
+                    "ours_GBps": alg / (res["ours_ms_per_step"] * 1e-3) / 1e9,
+                    "speedup": res["reference_ms_per_step"] / res["ours_ms_per_step"], "outputs_identical": bool(same)})
+        out[str(M)] = res
+        del wsp
+    return out
+
+
+def run_gpu_arm(args):
+    env = Env()
+    torch = env.torch
+    M = args.tokens
+    work, wbytes_total = build_workload(torch, args.layers, args.seed + 7919 * env.rank, env.device)
+    sampler = ClockSampler(env.local_rank)
+    if env.rank == 0:
+        sampler.start()
+    head, (xq, s, alg_step) = sweep_leg(env, work, M, args, headline=True)
+    e2e = e2e_leg(env, work, M, args, xq, s, alg_step)
+    clocks = sampler.stop() if env.rank == 0 else None
+
+    extras = {}
+    if not args.headline_only:
+        if env.world == 1:
+            extras["by_tokens"] = {}
+            for m in (1, 16):
+                if m != M:
+                    extras["by_tokens"][str(m)] = sweep_leg(env, work, m, args, headline=False)[0]
+            extras["ref_kernels_b200"] = ref_kernels_leg(env, work, args)
+        del work
+        torch.cuda.empty_cache()
+        if env.world == 1:
+            extras["decode"] = decode_leg(args)
+        else:
+            extras["tp"] = {mode: tp_stack(env, args, mode, 64, 4) for mode in ("single", "fused")}
+
+    if env.rank == 0:
         cpu_baseline = None            # timed at N = 1 only (rank 0's host cores)
-        if world == 1:
+        if env.world == 1:
             one_pass, cpu_alg, cores, reps, dt = cpu_sample(M, 10.0)
             t0 = time.perf_counter()
             for _ in range(reps):
@@ -361,57 +520,36 @@ def run_gpu_arm(args):
                             "sample": f"{reps} passes over one layer (4 linears) at {M} tokens, dense int8 ternary "
                                       f"weights, {cpu_dt:.1f} s"}
         line = {
-            "metric": "ternaspmm_algorithmic_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_max / args.steps,
+            "metric": "ternaspmm_algorithmic_GBps", "value": head["value"], "unit": "GB/s", "n_gpus": env.world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": head["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "int8xternary->int32->bf16", "data": "synthetic",
-            "config": {"workload": f"bitnet2b_linear_sweep_M{M}", "tokens": M, "layers": args.layers,
-                       "linears_per_step": launches, "p_zero": P_ZERO, "seed": args.seed,
-                       "compressed_weight_bytes_per_rank": wbytes_total,
-                       "l2_policy": "inputs larger than L2: each step streams %.0f MB of distinct weights" %
-                                    (wbytes_total / 1e6),
-                       "parallelism": "replicas only" if world > 1 else "single GPU",
-                       "launch": "one CUDA graph replay per step"},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "peak_kind": "of " + peak_kind,
-                         "frac_of_nominal_8000": achieved / 8000.0,
-                         "kernel": "spmm_small_m_kernel", "avg_launch_us": per_launch_us,
-                         "algorithmic_bytes_per_launch": alg_step / launches,
-                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(M)},
-            "cpu_baseline": cpu_baseline,
-            "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms / args.steps, "api": "ternainfer_b200.linear.TernaInfer_linear captured in a CUDA graph together with its H2D and (side-stream) D2H copies; one replay per step"},
-            "gpu_launches": launches * args.steps,
-            "clocks": clocks,
+            "config": sweep_config(args, env.world),
+            "launch": "one CUDA graph replay per step", "compressed_weight_bytes_per_rank": wbytes_total,
+            "roofline": head["roofline"], "cpu_baseline": cpu_baseline, "e2e": e2e,
+            "gpu_launches": head["gpu_launches"], "clocks": clocks,
         }
+        line.update(extras)
         print(json.dumps(line), flush=True)
-    _finish(world)
+    _finish(env.world)
 
 
 # ----------------------------------------------------------------------------
-# Tensor-parallel arm (BASELINE config 5 shapes): hidden 8192, 64/8 heads,
+# Tensor-parallel arm (the scaled ternary model): hidden 8192, 64/8 heads,
 # ffn 28672, batch 64.  Per layer: QKV and gate-up column-parallel, O and down
 # row-parallel with ONE all-reduce each; the attention itself is not part of
 # the path and is skipped (its output is a fixed synthetic tensor).  Strong
 # scaling: the model is fixed, each rank holds 1/N of every weight.
 # ----------------------------------------------------------------------------
 
-def run_tp_arm(args):
-    import torch
-    import torch.distributed as dist
-    from ternainfer_b200 import load_library, tp
+def tp_stack(env, args, mode, M, L):
+    """`L` layers of the 8192-wide model's four linears at `M` tokens, sharded over all ranks (see the
+    comment above).  Returns the timing of one step (all layers) as a dict."""
+    torch, dist = env.torch, env.dist
+    from ternainfer_b200 import tp
     from ternainfer_b200.convert import compress_weight, compressed_nbytes
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-    load_library()
-    dim, H, Hkv, D, ffn, M = 8192, 64, 8, 128, 28672, args.tokens if args.tokens != 8 else 64
-    L = args.layers if args.layers != 30 else 4
+    world, rank, device = env.world, env.rank, env.device
+    dim, H, Hkv, D, ffn = 8192, 64, 8, 128, 28672
     gen = torch.Generator(device=device)
 
     def tern(n, k, seed):
@@ -420,7 +558,7 @@ def run_tp_arm(args):
         sign = torch.randint(0, 2, (n, k), generator=gen, device=device, dtype=torch.int8) * 2 - 1
         return torch.where(r < P_ZERO, torch.zeros((), dtype=torch.int8, device=device), sign)
 
-    layers, wbytes = [], 0
+    layers, wbytes, dense0 = [], 0, {}
     for li in range(L):
         dic = {}
         specs = [("wqkv", "column", (H + 2 * Hkv) * D // world, dim, [H * D // world, Hkv * D // world, Hkv * D // world]),
@@ -434,24 +572,55 @@ def run_tp_arm(args):
             dic[name + ".weight_compressed_val"], dic[name + ".weight_TileOffsets_global"] = cv, tg
             dic[name + ".weight_TileOffsets_median"], dic[name + ".weight_bitmap"] = tm, bm
             ws = torch.zeros(4, device=device)
-            ws[:len(segs) if segs else 1] = 0.02
+            ws[:len(segs) if segs else 1] = torch.tensor([0.02, 0.03, 0.025][:len(segs) if segs else 1], device=device)
             dic[name + ".weight_scale"] = ws.to(torch.bfloat16)
             if segs:
                 dic[name + ".weight_segments"] = torch.tensor(segs)
+            if li == 0 and rank == 0:
+                dense0[name] = (w.cpu().numpy(), [dic[name + sfx] for sfx in (".weight_compressed_val", ".weight_TileOffsets_global",
+                                                                           ".weight_TileOffsets_median", ".weight_bitmap")],
+                                dic[name + ".weight_scale"], segs)
             del w
         ones_d = torch.ones(dim // world, device=device)
         ones_f = torch.ones(ffn // world, device=device)
         layers.append((tp.ColumnParallelSpBitLinear(dim, specs[0][2], dic, "wqkv"),
-                       tp.RowParallelSpBitLinear(dim // world, dim, dic, "wo", None, ones_d, 1e-5, args.tp_mode,
-                                                 max_tokens=M),
+                       tp.RowParallelSpBitLinear(dim // world, dim, dic, "wo", None, ones_d, 1e-5, mode, max_tokens=M),
                        tp.ColumnParallelSpBitLinear(dim, specs[2][2], dic, "w13"),
-                       tp.RowParallelSpBitLinear(ffn // world, dim, dic, "w2", None, ones_f, 1e-5, args.tp_mode,
+                       tp.RowParallelSpBitLinear(ffn // world, dim, dic, "w2", None, ones_f, 1e-5, mode,
                                                  gated=True, max_tokens=M)))
     gen.manual_seed(args.seed)
     x0 = torch.randn((M, dim), generator=gen, device=device).to(torch.bfloat16)
     attn = torch.randn((M, dim // world), generator=gen, device=device).to(torch.bfloat16)
     if world > 1:
         dist.broadcast(x0, 0)
+
+    # Sanity check outside the timed region (rank 0, layer 0): every shard's packed weight and the
+    # kernels that multiply it, against the CPU oracle - int32 accumulators of all four linears
+    # bit-exact, and the column-parallel QKV (explicit scale segments) bf16-identical.
+    if rank == 0:
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import ternaspmm_oracle as o
+        import c_oracle
+        one = np.full(M, 0x3F80, np.uint16)
+        for name, (wd, packed, ws, segs) in dense0.items():
+            n, k = wd.shape
+            xq = torch.randint(-128, 128, (M, k), dtype=torch.int8, device=device)
+            got = tp._accumulate_i32(xq, packed, n).cpu().numpy()
+            acc, _ = c_oracle.ternaspmm(xq.cpu().numpy(), wd, one, np.full(4, 0x3F80, np.uint16), 1)
+            if not (got == acc).all():
+                raise SystemExit(f"tp bench sanity check failed: int32 accumulators of {name} differ from the oracle")
+        wd, packed, ws, segs = dense0["wqkv"]
+        xq, s = tp._quant_fused(x0)
+        bounds = [sum(segs[:i + 1]) for i in range(2)]
+        got = tp._linear_segments(xq, s, packed, ws, bounds, wd.shape[0]).view(torch.int16).cpu().numpy().view(np.uint16)
+        acc = o.gemm_i32(xq.cpu().numpy(), wd) if wd.size < (1 << 26) else \
+            c_oracle.ternaspmm(xq.cpu().numpy(), wd, one, np.full(4, 0x3F80, np.uint16), 1)[0]
+        g = (np.arange(wd.shape[0]) >= bounds[0]).astype(np.int64) + (np.arange(wd.shape[0]) >= bounds[1])
+        v = (acc.astype(np.float32) / s.float().cpu().numpy().reshape(-1, 1)).astype(np.float32) * \
+            ws.float().cpu().numpy()[g][None, :]
+        if not (got == o.f32_to_bf16_bits(v)).all():
+            raise SystemExit("tp bench sanity check failed: sharded QKV output differs from the oracle")
+    dense0.clear()
 
     def step():
         x = x0
@@ -461,75 +630,69 @@ def run_tp_arm(args):
             x = w2(w13(h), residual=h)
         return x
 
-    def log(msg):
-        if rank == 0 and args.verbose:
-            print("[tp] " + msg, file=sys.stderr, flush=True)
-
     class _Eager:
         def replay(self):
             step()
 
-    stream = torch.cuda.Stream(device=device)
-    with torch.cuda.stream(stream):
-        log("weights built; eager warm-up")
+    with torch.cuda.stream(env.stream):
         for _ in range(2):
             step()
-        stream.synchronize()
-        log("eager steps done")
+        env.stream.synchronize()
         if args.no_graph:
             graph = _Eager()
         else:
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
+            with torch.cuda.graph(graph, stream=env.stream):
                 y = step()
-            log("graph captured")
-        for _ in range(args.warmup):
-            graph.replay()
-        log("warm-up replays done")
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-        sampler = ClockSampler(local_rank)
-        if rank == 0:
-            sampler.start()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(args.steps):
-            graph.replay()
-        e1.record(stream)
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
+    ms = env.time_replays(graph.replay, args.steps, args.warmup, min_load_s=0.3)
+    tp.check_status()     # a device-side wait that ran out would have poisoned the outputs
+    if not torch.isfinite(step().float()).all():
+        raise SystemExit("tp bench: non-finite outputs")
     wb = torch.tensor([float(wbytes)], dtype=torch.float64, device=device)
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.all_reduce(wb)
-    clocks = sampler.stop() if rank == 0 else None
-    if rank == 0:
-        ms = float(t.item())
+    peak, kind = measured_peak()
+    val = float(wb.item()) * args.steps / (ms * 1e-3) / 1e9
+    res = {"mode": mode, "ms_per_step": ms / args.steps, "layers": L, "tokens": M, "tp": world,
+           "compressed_weight_GBps": val, "per_gpu_frac": val / world / peak, "peak_kind": "of " + kind,
+           "collective": {"single": "one NCCL all-reduce per row-parallel linear",
+                          "fused": "reduce-scatter + all-gather inside the finish kernel over peer memory (plain NVLink "
+                                   "loads and stores)",
+                          "exact": "three all-reduces per row-parallel linear (bit-exact mode)"}[mode],
+           "gpu_launches": (6 if mode == "exact" else 10) * L * args.steps}
+    del layers, graph
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_tp_arm(args):
+    env = Env()
+    M = args.tokens if args.tokens != 8 else 64
+    L = args.layers if args.layers != 30 else 4
+    sampler = ClockSampler(env.local_rank)
+    if env.rank == 0:
+        sampler.start()
+    res = tp_stack(env, args, args.tp_mode, M, L)
+    clocks = sampler.stop() if env.rank == 0 else None
+    if env.rank == 0:
         peak, kind = measured_peak()
-        val = float(wb.item()) * args.steps / (ms * 1e-3) / 1e9
-        line = {"metric": "ternaspmm_tp_compressed_weight_GBps", "value": val, "unit": "GB/s", "n_gpus": world,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-                "scaling": "strong", "vs_baseline": None, "dtype": "int8xternary->int32->bf16", "data": "synthetic",
-                "config": {"workload": f"tp_linear_stack_8192x28672_bs{M}", "layers": L, "tokens": M, "tp": world,
-                           "row_parallel_mode": args.tp_mode,
-                           "collective": {"single": "one NCCL all-reduce per row-parallel linear",
-                                          "fused": "all-reduce inside the finish kernel over peer memory (plain NVLink loads)",
-                                          "exact": "three all-reduces per row-parallel linear (bit-exact mode)"}[args.tp_mode],
-                           "l2_policy": "inputs larger than L2: %.0f MB of weights per step over all ranks" % (wb.item() / 1e6)},
-                "roofline": {"bound": "hbm", "achieved": val / world, "peak": peak, "unit": "GB/s",
-                             "frac": val / world / peak, "peak_kind": "of " + kind, "traffic": None,
+        line = {"metric": "ternaspmm_tp_compressed_weight_GBps", "value": res["compressed_weight_GBps"], "unit": "GB/s",
+                "n_gpus": env.world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"],
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "int8xternary->int32->bf16", "data": "synthetic",
+                "config": {"workload": f"tp_linear_stack_8192x28672_bs{M}", "layers": L, "tokens": M, "tp": env.world,
+                           "row_parallel_mode": args.tp_mode, "collective": res["collective"],
+                           "l2_policy": "inputs larger than L2: every step streams all layers' weight shards"},
+                "roofline": {"bound": "hbm", "achieved": res["compressed_weight_GBps"] / env.world, "peak": peak,
+                             "unit": "GB/s", "frac": res["per_gpu_frac"], "peak_kind": "of " + kind, "traffic": None,
                              "note": "per-GPU compressed-weight bytes per second"},
-                "gpu_launches": (6 if args.tp_mode == "exact" else 10) * L * args.steps, "clocks": clocks}
+                "gpu_launches": res["gpu_launches"], "clocks": clocks}
         print(json.dumps(line), flush=True)
-    _finish(world)
+    _finish(env.world)
 
 
 # ----------------------------------------------------------------------------
-# End-to-end decode arm (BASELINE config 4): the 30-layer BitNet-2B architecture
+# End-to-end decode arm: the 30-layer BitNet-2B architecture
 # with random-init ternary weights and a dense bf16 tied embedding / head, prompt
 # of seeded random ids, greedy generation; value = decode tokens per second.
 # ----------------------------------------------------------------------------
@@ -544,6 +707,7 @@ def cpu_decode_sample(bsz, layers, seconds_budget=10.0, seed=1234):
     import torch.nn.functional as F
     torch.manual_seed(seed)
     dim, H, Hkv, D, ffn, vocab, L = 2560, 20, 5, 128, 6912, 128256, 640
+    torch.set_num_threads(os.cpu_count() or 1)    # launchers export OMP_NUM_THREADS=1; use the host's cores
     cores = torch.get_num_threads()
 
     def tern(n, k):
@@ -595,26 +759,52 @@ def cpu_decode_sample(bsz, layers, seconds_budget=10.0, seed=1234):
                                f"float32 torch CPU ops; step = {layers} x layer + head"
 
 
-def run_decode_arm(args):
+def decode_run(args, bsz, fused, reps):
+    """Greedy generation of 128 tokens after a 512-token prompt at batch `bsz`; best of `reps` runs."""
     import torch
     from ternainfer_b200.generate import FastGen, GenArgs, build_random_model
     from ternainfer_b200.model import ModelArgs
-    torch.cuda.set_device(0)
-    bsz = args.tokens if args.tokens in (1, 8) else 1
-    margs = ModelArgs(n_layers=args.layers, fused_glue=not args.unfused)
+    margs = ModelArgs(n_layers=args.layers, fused_glue=fused)
     model, _ = build_random_model(margs, 512 + 128, args.seed)
     gen = FastGen(model, GenArgs(128, bsz, 512, True))
     g = torch.Generator(device="cuda").manual_seed(args.seed + 1)
     prompt = torch.randint(0, margs.vocab_size, (bsz, 512), generator=g, device="cuda")
-    for _ in range(max(1, args.warmup // 3)):
-        gen.generate(prompt)
-    sampler = ClockSampler(0)
-    sampler.start()
-    best = None
-    for _ in range(max(1, args.steps // 10)):
-        _, st = gen.generate(prompt)
+    gen.generate(prompt)            # captures the graphs
+    best, first = None, None
+    for _ in range(reps):
+        toks, st = gen.generate(prompt)
+        first = toks[0, :8].tolist()
         if best is None or st["decode_tokens_per_s"] > best["decode_tokens_per_s"]:
             best = st
+    del gen, model
+    torch.cuda.empty_cache()
+    return best, first
+
+
+def decode_leg(args):
+    """Decode tokens/s of the 30-layer model (prompt 512, 128 generated tokens) at batch 1 and 8, with
+    the fused front-ends and with plain torch glue between the linears, plus the PyTorch-CPU decode step."""
+    out = {"layers": args.layers, "prompt": 512, "generate": 128}
+    for bsz in (1, 8):
+        entry = {}
+        for fused in (True, False):
+            st, first = decode_run(args, bsz, fused, 2)
+            entry["fused_glue" if fused else "torch_glue"] = {
+                "decode_tokens_per_s": st["decode_tokens_per_s"], "prefill_tokens_per_s": st["prefill_tokens_per_s"],
+                "first_tokens": first}
+        cpu_tps, cores, sample = cpu_decode_sample(bsz, args.layers, seconds_budget=6.0)
+        entry["cpu_baseline"] = {"value": cpu_tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+        out[f"bs{bsz}"] = entry
+    return out
+
+
+def run_decode_arm(args):
+    import torch
+    torch.cuda.set_device(0)
+    bsz = args.tokens if args.tokens in (1, 8) else 1
+    sampler = ClockSampler(0)
+    sampler.start()
+    best, _ = decode_run(args, bsz, not args.unfused, max(1, args.steps // 10))
     clocks = sampler.stop()
     line = {"metric": "decode_tokens_per_s", "value": best["decode_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * bsz / best["decode_tokens_per_s"],
@@ -658,6 +848,8 @@ def main():
     ap.add_argument("--tp_mode", default="single", choices=["single", "fused", "exact"])
     ap.add_argument("--no_graph", action="store_true", help="tp workload: launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--headline_only", action="store_true",
+                    help="sweep workload: only the headline and end-to-end legs (short runs for profiling)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

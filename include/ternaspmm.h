@@ -213,6 +213,20 @@ void ternaspmm_tp_allreduce_finish(float** bufs, unsigned int** flags, ternaspmm
                                    int full_width, int M, int N, ternaspmm_bf16* residual,
                                    ternaspmm_stream_t stream);
 
+/* Output head for decode-sized batches: logits[t][v] = sum_k h[t][k] * embedding[v][k] for
+ * 1 <= M <= 8 rows of hidden states, bf16 inputs, fp32 accumulation, and the greedy token per
+ * row, in one launch that reads the embedding once.  Replaces the dense bf16 GEMM over the tied
+ * embedding (model.py:367, :385 of the reference) plus the torch.argmax of its generation loop
+ * (generate.py:283, :305) for decode steps.  logits: fp32 [M][V] or null; with round_bf16 != 0
+ * every value is rounded to bf16 first, as the reference's bf16 linear returns it.  argmax:
+ * int64 [M] or null: index of the largest (rounded) logit, smallest index on ties.  scratch:
+ * ternaspmm_lm_head_scratch_bytes() bytes of device memory, zero-initialised once by the caller
+ * (the kernel leaves its counter at zero); calls that share a scratch area must not overlap on
+ * the GPU.  K a multiple of 32, at most 12288; h, embedding and scratch 16-byte aligned. */
+void ternaspmm_lm_head_argmax(ternaspmm_bf16* h, ternaspmm_bf16* embedding, int M, int V, int K, float* logits,
+                              long long* argmax, int round_bf16, void* scratch, ternaspmm_stream_t stream);
+long long ternaspmm_lm_head_scratch_bytes(void);
+
 /* Host packer from int8 ternary [N][K] into caller-provided arrays
  * (bitmap N*K/64, tile_offsets tiles+1, quarter_offsets 3*tiles, sign_words
  * at least N*K/32 + 4 words, zero-filled by the call).  Returns the number of

@@ -24,6 +24,7 @@ def load():
         lib = ctypes.CDLL(path)
         P, I = ctypes.c_void_p, ctypes.c_int
         lib.oracle_num_threads.restype = I
+        lib.oracle_set_num_threads.argtypes = [I]
         lib.oracle_gemm_i32.argtypes = [P, P, I, I, I, P]
         lib.oracle_epilogue.argtypes = [P, P, P, I, I, I, I, P]
         lib.oracle_ternaspmm.argtypes = [P, P, P, P, I, I, I, I, I, P, P]

@@ -60,3 +60,20 @@ extern "C" int ref_bitlinear_TernaSpMM_decode(int8_t* x, uint64_t* bitmap, int* 
     SplitK_Reduction<<<dim3(n_out * tokens / 256, 1, 1), dim3(WARP_SIZE, 1, 1), 0, st>>>(out, workspace, n_out, tokens, split_k, s, ws, ws_num);
     return (int)cudaGetLastError();
 }
+
+// The reference's prefill stage 1 (kernels/src/SpMM/SpMM_Kernel.cuh:165-295, launched as in
+// kernels/src/TernaSpMM_API.cuh:139-162): decompress the packed weight into a dense row-major
+// int8 matrix dense[n_out][k] (the operand its CUTLASS GEMM then reads).  Needs no CUTLASS, so it
+// pins the packed FORMAT of the prefill path with the reference's own code; the GEMM and its
+// epilogue visitor cannot be built here.  Returns a CUDA error code.
+extern "C" int ref_decompress_prefill(uint64_t* bitmap, int* tile_off, uint16_t* med_off, uint32_t* vals,
+                                      int8_t* dense, int n_out, int k, int split_k, cudaStream_t st) {
+    using Cfg = TilingConfigBitmapV3<4, 1, 1>;
+    const int smem = Cfg::MY_MAX_INT8_NNZS_INTILE * 2 + Cfg::TILE_BITMAP_M_V3 * Cfg::TILE_BITMAP_K_V3 * 8;
+    cudaError_t e = cudaFuncSetAttribute(mySpMM_Kernel_bitmap_prefill<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid(1, n_out * split_k / Cfg::TILE_M, 1), block(WARP_SIZE * Cfg::BLOCK_WARPS, 1, 1);
+    mySpMM_Kernel_bitmap_prefill<Cfg><<<grid, block, smem, st>>>(vals, tile_off, med_off, bitmap,
+                                                                 reinterpret_cast<int32_t*>(dense), n_out, 1, k, split_k);
+    return (int)cudaGetLastError();
+}

@@ -41,6 +41,11 @@ static inline uint16_t f32_to_bf16_rn(float f) {
     return (uint16_t)(u >> 16);
 }
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; a timing run sets the thread count itself. */
+void oracle_set_num_threads(int n) {
+    if (n > 0) omp_set_num_threads(n);
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

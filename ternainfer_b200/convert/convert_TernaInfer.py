@@ -135,6 +135,8 @@ def random_checkpoint(dim: int, n_layers: int, n_heads: int, n_kv_heads: int, ff
             dic[key + ".weight_compressed_val"], dic[key + ".weight_TileOffsets_global"] = cv, tg
             dic[key + ".weight_TileOffsets_median"], dic[key + ".weight_bitmap"] = tm, bm
             dic[key + ".weight_scale"] = ws.to(torch.bfloat16)
+            if len(segs) > 1:
+                dic[key + ".weight_segments"] = torch.tensor(segs, dtype=torch.int64)
             if dense:
                 rows = torch.repeat_interleave(ws[:len(segs)], torch.tensor(segs, device=device))
                 dic[key + ".weight"] = (w.float() * rows[:, None]).to(torch.bfloat16)

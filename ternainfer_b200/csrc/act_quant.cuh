@@ -9,7 +9,13 @@
 // HBM traffic is one read of the activations and one write of int8 + scale.
 // Rounding points follow the eager PyTorch evaluation of the same expressions
 // (bf16 after the norm, bf16(1/amax) * 127 for the scale, bf16(x*s) before the
-// round-half-even), the sum of squares is accumulated in fp32.
+// round-half-even).  The fp32 sum of squares has a FIXED order, so the result is
+// reproducible bit for bit by any implementation that follows it: with T
+// threads, thread t adds f*f (product rounded, then sum rounded: no fused
+// multiply-add) over elements (j*T + t)*8 + 0..7 for j = 0, 1, ...; the 32
+// lanes of a warp combine by the xor butterfly 16, 8, 4, 2, 1; warp sums are
+// added in warp order.  The RMS factor is 1 / sqrt(ss / K + eps) with IEEE
+// division and square root.  T = min(1024, max(64, K/8 rounded up to 32)).
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -81,14 +87,14 @@ __global__ void __launch_bounds__(kActMaxThreads) norm_quant_kernel(const __nv_b
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const float f = __bfloat162float(v[i]);
-            ss += f * f;
+            ss = __fadd_rn(ss, __fmul_rn(f, f));
         }
         *reinterpret_cast<uint4*>(row + k0) = *reinterpret_cast<const uint4*>(v);
     }
     float rstd = 1.f;
     if (MODE != ACT_PLAIN) {
         ss = block_reduce(ss, scratch, false);
-        if (MODE == ACT_RMSNORM) rstd = rsqrtf(ss / (float)K + eps);
+        if (MODE == ACT_RMSNORM) rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)K), eps)));
         if (MODE == ACT_SCALE_SUMSQ && tid == 0) ss_out[t] = ss;
     }
 
@@ -102,8 +108,8 @@ __global__ void __launch_bounds__(kActMaxThreads) norm_quant_kernel(const __nv_b
             const __nv_bfloat16* ww = reinterpret_cast<const __nv_bfloat16*>(&wv);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const float y = (MODE == ACT_RMSNORM ? __bfloat162float(av[i]) * rstd : __bfloat162float(av[i])) *
-                                __bfloat162float(ww[i]);
+                const float y = __fmul_rn(MODE == ACT_RMSNORM ? __fmul_rn(__bfloat162float(av[i]), rstd) : __bfloat162float(av[i]),
+                                          __bfloat162float(ww[i]));
                 av[i] = __float2bfloat16_rn(y);
             }
             *reinterpret_cast<uint4*>(row + k0) = a;

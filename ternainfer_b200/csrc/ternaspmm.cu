@@ -13,6 +13,7 @@
 #include <algorithm>
 
 #include "act_quant.cuh"
+#include "lm_head.cuh"
 #include "spmm_large_m.cuh"
 #include "spmm_small_m.cuh"
 
@@ -608,6 +609,55 @@ extern "C" void ternaspmm_tp_allreduce_finish(float** bufs, unsigned int** flags
                            (const __nv_bfloat16*)ws, eps, full_width, M, N, (const __nv_bfloat16*)residual,
                            status, g_wait_limit_ns) != cudaSuccess)
         t_host_status = ST_LAUNCH;
+    checkLastCudaError(__LINE__);
+}
+
+extern "C" long long ternaspmm_lm_head_scratch_bytes(void) { return (long long)kHeadScratchBytes; }
+
+extern "C" void ternaspmm_lm_head_argmax(__nv_bfloat16* h, __nv_bfloat16* embedding, int M, int V, int K, float* logits,
+                                        long long* argmax, int round_bf16, void* scratch, cudaStream_t stream) {
+    t_host_status = ST_OK;
+    if (M < 1 || M > 8 || V < 1 || K < 32 || (K % 32) || K > 12288) {
+        fprintf(stderr, "ternaspmm: lm_head_argmax needs 1 <= M <= 8, V >= 1, K a multiple of 32 up to 12288 (got M=%d V=%d K=%d)\n",
+                M, V, K);
+        t_host_status = ST_BAD_SHAPE;
+        return;
+    }
+    if (!h || !embedding || (!logits && !argmax) || (argmax && !scratch) || (reinterpret_cast<uintptr_t>(h) & 15) ||
+        (reinterpret_cast<uintptr_t>(embedding) & 15) || (reinterpret_cast<uintptr_t>(scratch) & 15)) {
+        fprintf(stderr, "ternaspmm: lm_head_argmax: null or misaligned pointer (h, embedding, scratch: 16 bytes)\n");
+        t_host_status = ST_BAD_POINTER;
+        return;
+    }
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!attr_done[dev]) {
+        if (cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * (12288 * 2 + 64)) != cudaSuccess) {
+            t_host_status = ST_LAUNCH;
+            return;
+        }
+        attr_done[dev] = true;
+    }
+    HeadParams p;
+    p.h = h, p.emb = embedding, p.logits = logits, p.argmax = argmax;
+    p.counter = reinterpret_cast<unsigned int*>(scratch);
+    p.cand = reinterpret_cast<HeadCandidate*>(reinterpret_cast<uint8_t*>(scratch) + 16);
+    p.M = M, p.V = V, p.K = K, p.round_bf16 = round_bf16;
+    const int groups = (V + 15) / 16;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(std::min(std::min(device_sm_count(), groups), kHeadMaxCtas), 1, 1);
+    cfg.blockDim = dim3(kHeadWarps * 32, 1, 1);
+    cfg.dynamicSmemBytes = 8 * (K * 2 + 64);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tuning().pdl ? 1 : 0;
+    t_echo = {4, 8, 1, kHeadWarps, 0, (int)cfg.gridDim.x};
+    if (cudaLaunchKernelEx(&cfg, lm_head_kernel, p) != cudaSuccess) t_host_status = ST_LAUNCH;
     checkLastCudaError(__LINE__);
 }
 

@@ -3,8 +3,9 @@
 Mirrors ``generate.py`` of Gu-J/TernaInfer in what matters for the hot path:
 the prefill forward and the one-token decode forward are each captured into a
 CUDA graph after a warm-up forward (:121-154, :192-224) and replayed with
-static input tensors, greedy sampling is an argmax over fp32 logits (:283,
-:305), and throughput is reported per phase.  Tokenizer, chat format and top-p
+static input tensors, greedy sampling is an argmax over the logits of each
+sequence's last position (:274, :283, :305) - taken inside the output-head
+kernel, so the graphs return token ids - and throughput is reported per phase.  Tokenizer, chat format and top-p
 sampling of the reference are not rebuilt: prompts are token ids.
 """
 from __future__ import annotations
@@ -37,22 +38,22 @@ class FastGen:
         self._tokens = torch.zeros((a.gen_bsz, 1), dtype=torch.long, device=self.device)
         self._pos = torch.zeros(1, dtype=torch.long, device=self.device)
         self._prefill_graph = self._decode_graph = None
-        self._prefill_logits = self._decode_logits = None
+        self._prefill_next = self._decode_next = None
 
     @torch.inference_mode()
     def _capture(self):
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):          # warm-up forwards outside capture (one-time library set-up)
-            self.model(self._prefill_tokens, self.cache, self._prefill_pos)
-            self.model(self._tokens, self.cache, self._pos)
+            self.model(self._prefill_tokens, self.cache, self._prefill_pos, greedy_last=True)
+            self.model(self._tokens, self.cache, self._pos, greedy_last=True)
         torch.cuda.current_stream().wait_stream(s)
         self._prefill_graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self._prefill_graph):
-            self._prefill_logits = self.model(self._prefill_tokens, self.cache, self._prefill_pos)[:, -1]
+            self._prefill_next = self.model(self._prefill_tokens, self.cache, self._prefill_pos, greedy_last=True)
         self._decode_graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self._decode_graph):
-            self._decode_logits = self.model(self._tokens, self.cache, self._pos)[:, -1]
+            self._decode_next = self.model(self._tokens, self.cache, self._pos, greedy_last=True)
 
     @torch.inference_mode()
     def generate(self, prompt: torch.Tensor):
@@ -66,10 +67,9 @@ class FastGen:
         self._prefill_tokens.copy_(prompt)
         if a.use_cuda_graph:
             self._prefill_graph.replay()
-            logits = self._prefill_logits
+            nxt = self._prefill_next
         else:
-            logits = self.model(self._prefill_tokens, self.cache, self._prefill_pos)[:, -1]
-        nxt = logits.argmax(-1)
+            nxt = self.model(self._prefill_tokens, self.cache, self._prefill_pos, greedy_last=True)
         torch.cuda.synchronize()
         t1 = time.perf_counter()
         for i in range(a.gen_length):
@@ -80,10 +80,9 @@ class FastGen:
             self._pos.fill_(a.prompt_length + i)
             if a.use_cuda_graph:
                 self._decode_graph.replay()
-                logits = self._decode_logits
+                nxt = self._decode_next
             else:
-                logits = self.model(self._tokens, self.cache, self._pos)[:, -1]
-            nxt = logits.argmax(-1)
+                nxt = self.model(self._tokens, self.cache, self._pos, greedy_last=True)
         torch.cuda.synchronize()
         t2 = time.perf_counter()
         stats = {"prefill_s": t1 - t0, "decode_s": t2 - t1,

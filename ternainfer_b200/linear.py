@@ -62,6 +62,33 @@ def rmsnorm_quant(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, gated:
     return q.reshape(*x.shape[:-1], K), s.reshape(*x.shape[:-1], 1)
 
 
+_HEAD_SCRATCH = {}
+
+
+def lm_head_argmax(h: torch.Tensor, embedding: torch.Tensor, want_logits: bool = True, want_argmax: bool = True):
+    """Output head for up to 8 rows: (fp32 logits [M, V] or None, int64 greedy tokens [M] or None).
+    One kernel that reads the embedding once; the logits carry the bf16 rounding of the reference's
+    bf16 linear and the arg-max is taken over them (smallest index on ties)."""
+    if not h.is_cuda:
+        raise RuntimeError("lm_head_argmax needs CUDA tensors: the B200 library has no CPU path")
+    lib = load_library()
+    V, K = embedding.shape
+    h2 = h.reshape(-1, K).contiguous()
+    M = h2.shape[0]
+    assert 1 <= M <= 8 and h2.dtype == torch.bfloat16 and embedding.dtype == torch.bfloat16 and embedding.is_contiguous()
+    dev = h.device
+    scratch = _HEAD_SCRATCH.get(dev)
+    if scratch is None:   # one zero-initialised scratch area per device (calls on one device run in stream order)
+        scratch = _HEAD_SCRATCH[dev] = torch.zeros(int(lib.ternaspmm_lm_head_scratch_bytes()), dtype=torch.uint8, device=dev)
+    logits = torch.empty((M, V), dtype=torch.float32, device=dev) if want_logits else None
+    tokens = torch.empty((M,), dtype=torch.int64, device=dev) if want_argmax else None
+    lib.ternaspmm_lm_head_argmax(h2.data_ptr(), embedding.data_ptr(), M, V, K,
+                                 logits.data_ptr() if want_logits else None,
+                                 tokens.data_ptr() if want_argmax else None, 1, scratch.data_ptr(),
+                                 torch.cuda.current_stream().cuda_stream)
+    return logits, tokens
+
+
 def TernaInfer_linear(input, compressed_val, TileOffsets_global, TileOffsets_median, bitmap,
                       workspace, s, ws, ws_num, out_features, mode: str = "auto", residual=None, segments=None):
     """out = TernaSpMM(input_int8, packed weight) as bf16 (model.py:45-92).

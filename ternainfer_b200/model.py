@@ -20,7 +20,7 @@ import torch
 from torch import nn
 from torch.nn import functional as F
 
-from .linear import SpBitLinear, quant_input, rmsnorm_quant
+from .linear import SpBitLinear, quant_input, rmsnorm_quant, lm_head_argmax
 
 
 @dataclass
@@ -35,6 +35,7 @@ class ModelArgs:
     rope_theta: float = 500000.0
     use_kernel: bool = True
     fused_glue: bool = False     # fused norm+quantiser kernels and residual add in the linear epilogue
+    flash_attention: Optional[bool] = None   # attention glue through flash_attn's kv-cache kernel; None = with fused_glue
 
     @property
     def head_dim(self) -> int:
@@ -126,7 +127,7 @@ class Attention(nn.Module):
         from flash_attn import flash_attn_with_kvcache
         B, T = x.shape[0], x.shape[1]
         H, Hkv, D = self.n_heads, self.n_kv_heads, self.head_dim
-        qkv = self.wqkv.forward_quantized(fused[0], fused[1])
+        qkv = self.wqkv(x) if fused is None else self.wqkv.forward_quantized(fused[0], fused[1])
         q = qkv[..., : H * D].view(B, T, H, D)
         k = qkv[..., H * D: (H + Hkv) * D].view(B, T, Hkv, D)
         v = qkv[..., (H + Hkv) * D:].view(B, T, Hkv, D)
@@ -193,7 +194,10 @@ class TransformerBlock(nn.Module):
                 h = self.attention(x, cache, pos, cos, sin, mask, fused=(xq, s, x, eps))
             hq, hs = rmsnorm_quant(h, self.ffn_norm.weight, eps)
             return self.feed_forward.forward_fused(hq, hs, h, eps)
-        h = x + self.attention(self.attention_norm(x), cache, pos, cos, sin, mask)
+        if flash is not None:
+            h = x + self.attention.forward_flash(self.attention_norm(x), cache, flash[0], flash[1], flash[2], None)
+        else:
+            h = x + self.attention(self.attention_norm(x), cache, pos, cos, sin, mask)
         return h + self.feed_forward(self.ffn_norm(h))
 
 
@@ -219,24 +223,43 @@ class Transformer(nn.Module):
         self.tp = tp
         self._rope = None
         self.flash = False
-        if args.fused_glue and tp == 1:
+        want_flash = args.fused_glue if args.flash_attention is None else args.flash_attention
+        if want_flash and tp == 1:
             try:
                 import flash_attn  # noqa: F401
                 self.flash = True
             except Exception:
+                if args.flash_attention:
+                    raise
                 self.flash = False
 
     def make_cache(self, batch: int, device, dtype=torch.bfloat16) -> List[LayerCache]:
         a = self.args
         shape = (batch, a.n_kv_heads // self.tp, self.max_seq_len, a.head_dim)
-        if self.flash and self.args.fused_glue:
+        if self.flash:
             shape = (batch, self.max_seq_len, a.n_kv_heads, a.head_dim)
         return [(torch.zeros(shape, device=device, dtype=dtype), torch.zeros(shape, device=device, dtype=dtype))
                 for _ in range(a.n_layers)]
 
-    def forward(self, tokens: torch.Tensor, cache: List[LayerCache], pos: torch.Tensor) -> torch.Tensor:
+    def head(self, h: torch.Tensor, greedy: bool = False):
+        """Final norm + tied output head.  fp32 logits [B, T, vocab] (model.py:380-386 of the
+        reference); with ``greedy`` -> (None, int64 tokens [B, T]) without materialising the logits.
+        Up to 8 rows run on the library's head kernel (one pass over the embedding, arg-max fused);
+        more rows use the dense bf16 GEMM."""
+        B, T = h.shape[0], h.shape[1]
+        h = self.norm(h)
+        emb = self.tok_embeddings.weight
+        if h.is_cuda and B * T <= 8 and emb.dtype == torch.bfloat16 and h.dtype == torch.bfloat16 and h.shape[-1] % 32 == 0:
+            logits, toks = lm_head_argmax(h, emb, want_logits=not greedy, want_argmax=greedy)
+            return (None, toks.view(B, T)) if greedy else logits.view(B, T, -1)
+        logits = F.linear(h, emb).float()
+        return (None, logits.argmax(-1)) if greedy else logits
+
+    def forward(self, tokens: torch.Tensor, cache: List[LayerCache], pos: torch.Tensor, greedy_last: bool = False):
         """tokens [B, T]; pos [T] (device int64) = positions written in the cache.
-        Returns fp32 logits [B, T, vocab] (model.py:380-386 of the reference)."""
+        Returns fp32 logits [B, T, vocab] (model.py:380-386 of the reference); with ``greedy_last``
+        only the greedy token of every sequence's last position, int64 [B] (what the generation
+        loop needs: generate.py:274, :283, :305 of the reference)."""
         if self._rope is None or self._rope[0].device != tokens.device:
             self._rope = rope_tables(self.args.head_dim, self.max_seq_len, self.args.rope_theta, tokens.device)
             self._rope_lp = (self._rope[0].to(torch.bfloat16), self._rope[1].to(torch.bfloat16))
@@ -247,9 +270,10 @@ class Transformer(nn.Module):
         h = self.tok_embeddings(tokens)
         fused = self.args.fused_glue and self.tp == 1
         flash = None
-        if fused and self.flash:
+        if self.flash:
             flash = (pos[:1].to(torch.int32).expand(B).contiguous(), self._rope_lp[0], self._rope_lp[1])
         for layer, c in zip(self.layers, cache):
             h = layer(h, c, pos, cos, sin, mask, fused, flash)
-        h = self.norm(h)
-        return F.linear(h, self.tok_embeddings.weight).float()
+        if greedy_last:
+            return self.head(h[:, -1:], greedy=True)[1][:, 0]
+        return self.head(h)

@@ -52,4 +52,7 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TERNAINFER_REFERENCE")
+    if not root:
+        sys.exit("usage: make_golden.py <path of the Gu-J/TernaInfer checkout>  (or set TERNAINFER_REFERENCE)")
+    main(root)

@@ -35,7 +35,7 @@ def check(lib, M, N, K, ws_num, entry="bitlinear_TernaSpMM", p_zero=0.45, seed=1
 
 @pytest.mark.parametrize("M", [1, 2, 3, 7, 8, 9, 15, 16, 17, 31, 32, 33, 64])
 def test_config1_shape_all_small_token_counts(lib, M):
-    # BASELINE config 1: N = K = 2560, P(0) = 0.45, per-tensor scale
+    # the single call of the reference's kernel test: N = K = 2560, P(0) = 0.45, per-tensor scale
     check(lib, M, 2560, 2560, 1)
 
 
@@ -272,7 +272,7 @@ def test_large_batch_both_epilogues_and_segments(lib, entry):
 
 
 def test_full_size_prefill_against_c_oracle(lib):
-    """BASELINE config 2's largest case: gate-up 2560 -> 13824 at 2048 tokens."""
+    """The largest case of the layer sweep: gate-up 2560 -> 13824 at 2048 tokens."""
     N, K, M = 13824, 2560, 2048
     w = o.make_ternary(N, K, 0.45, seed=61)
     xq, s = o.make_activations(M, K, seed=62)

@@ -123,8 +123,15 @@ def _leaving_worker(rank, world, port, q):
     x = torch.randn(M, ffn // world).to(torch.bfloat16)
     y = row(x)                       # step 1: both ranks take part
     dist.barrier()
-    if rank == 1:
+    # rank 1 leaves only once rank 0 is known (through the store, on the host) to be out of the
+    # barrier: nothing of step 1 is in flight any more
+    store = dist.distributed_c10d._get_default_store()
+    if rank == 0:
+        store.set("rank0_past_step1", "1")
+    else:
+        store.wait(["rank0_past_step1"])
         os._exit(0)                  # leaves between steps
+    time.sleep(0.5)
     t0 = time.monotonic()
     try:
         row(x)                       # step 2: the peer is gone
