@@ -481,6 +481,90 @@ def ref_kernels_leg(env, work, args):
     return out
 
 
+def list_leg(env, work, M, args):
+    """The same step through the work-list entry points: all linears of the step in ONE persistent
+    launch (ternaspmm_list_run), inputs resident in HBM, replayed as a CUDA graph."""
+    torch, lib = env.torch, env.lib
+    from ternainfer_b200.lib import ListItem
+    xq, s = quantised_inputs(env, M, args.seed)
+    outs = [torch.empty((M, it["N"]), dtype=torch.bfloat16, device=env.device) for it in work]
+    arr = (ListItem * len(work))()
+    for a, it, out in zip(arr, work, outs):
+        K = it["K"]
+        a.x, a.bitmap, a.tile_offsets, a.quarter_offsets = xq[K].data_ptr(), it["bm"].data_ptr(), it["tg"].data_ptr(), it["tm"].data_ptr()
+        a.sign_words, a.out, a.s, a.ws, a.residual = it["cv"].data_ptr(), out.data_ptr(), s[K].data_ptr(), it["ws"].data_ptr(), None
+        a.ws_num, a.M, a.N, a.K, a.seg1, a.seg2, a.seg3, a.prefill_form = it["ws_num"], M, it["N"], K, 0, 0, 0, -1
+    tb, sb = ctypes.c_longlong(), ctypes.c_longlong()
+    entries = lib.ternaspmm_list_plan(arr, len(work), ctypes.byref(tb), ctypes.byref(sb))
+    if entries < 0:
+        raise SystemExit("bench: the work list was rejected")
+    table = torch.empty(tb.value, dtype=torch.uint8, device=env.device)
+    scratch = torch.empty(sb.value, dtype=torch.uint8, device=env.device)
+    with torch.cuda.stream(env.stream):
+        handle = lib.ternaspmm_list_create(arr, len(work), table.data_ptr(), scratch.data_ptr(), env.stream.cuda_stream)
+        if not handle:
+            raise SystemExit("bench: could not create the work list")
+        lib.ternaspmm_list_run(handle, env.stream.cuda_stream)
+    env.stream.synchronize()
+    check_layer0_against_oracle(env, work, outs, xq, s)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(env.stream):
+        with torch.cuda.graph(graph, stream=env.stream):
+            lib.ternaspmm_list_run(handle, env.stream.cuda_stream)
+    ms = env.time_replays(graph.replay, args.steps, args.warmup, min_load_s=0.3)
+    if lib.ternaspmm_last_status() != 0:
+        raise SystemExit("bench: the work-list run reported a non-zero status")
+    lib.ternaspmm_list_destroy(handle)
+    alg_step = sum(algorithmic_bytes(it, M) for it in work)
+    peak, peak_kind = measured_peak()
+    achieved = alg_step * args.steps / (ms * 1e-3) / 1e9
+    return {"value": achieved * env.world, "unit": "GB/s", "ms_per_step": ms / args.steps, "items": len(work),
+            "entries": entries, "tokens": M,
+            "api": "ternaspmm_list_run: one persistent launch per step over all of the step's linears",
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": "of " + peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
+                         "kernel": "spmm_list_kernel", "avg_launch_us": ms * 1e3 / args.steps,
+                         "avg_item_us": ms * 1e3 / args.steps / len(work), "algorithmic_bytes_per_launch": alg_step,
+                         "traffic": ncu_traffic("spmm_list_kernel", M)},
+            "gpu_launches": args.steps}
+
+
+def lm_head_leg(env, args):
+    """The output-head kernel alone: logits-free greedy token of M rows over the 128256 x 2560 bf16
+    embedding (657 MB, five times the L2: every call streams it from HBM)."""
+    torch, lib = env.torch, env.lib
+    V, K = 128256, 2560
+    g = torch.Generator(device=env.device).manual_seed(args.seed)
+    emb = (0.02 * torch.randn((V, K), generator=g, device=env.device)).to(torch.bfloat16)
+    scratch = torch.zeros(int(lib.ternaspmm_lm_head_scratch_bytes()), dtype=torch.uint8, device=env.device)
+    peak, peak_kind = measured_peak()
+    out = {}
+    for M in (1, 8):
+        h = torch.randn((M, K), generator=g, device=env.device).to(torch.bfloat16)
+        toks = torch.empty(M, dtype=torch.int64, device=env.device)
+
+        def run():
+            lib.ternaspmm_lm_head_argmax(h.data_ptr(), emb.data_ptr(), M, V, K, None, toks.data_ptr(), 1,
+                                         scratch.data_ptr(), torch.cuda.current_stream().cuda_stream)
+
+        with torch.cuda.stream(env.stream):
+            run()
+        env.stream.synchronize()
+        want = torch.nn.functional.linear(h, emb).float()
+        picked = want.gather(1, toks.view(-1, 1)).view(-1)
+        if not (want.max(dim=1).values - picked <= want.abs().max() * 2.0 ** -6).all():
+            raise SystemExit("bench: the head kernel's greedy tokens disagree with the dense product")
+        ms = env.time_replays(run, args.steps, args.warmup)
+        nbytes = V * K * 2 + M * K * 2 + 8 * M
+        gbs = nbytes * args.steps / (ms * 1e-3) / 1e9
+        dense_ms = env.time_replays(lambda: torch.nn.functional.linear(h, emb).float().argmax(-1), args.steps, args.warmup)
+        out[str(M)] = {"us_per_call": ms * 1e3 / args.steps, "GBps": gbs, "frac": gbs / peak, "peak_kind": "of " + peak_kind,
+                       "algorithmic_bytes": nbytes, "torch_bf16_linear_plus_argmax_us": dense_ms * 1e3 / args.steps}
+    del emb
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_gpu_arm(args):
     env = Env()
     torch = env.torch
@@ -495,15 +579,19 @@ def run_gpu_arm(args):
 
     extras = {}
     if not args.headline_only:
+        if M <= 16:
+            extras["list_entry"] = list_leg(env, work, M, args)
         if env.world == 1:
             extras["by_tokens"] = {}
             for m in (1, 16):
                 if m != M:
                     extras["by_tokens"][str(m)] = sweep_leg(env, work, m, args, headline=False)[0]
+                    extras["by_tokens"][str(m)]["list_entry"] = list_leg(env, work, m, args)
             extras["ref_kernels_b200"] = ref_kernels_leg(env, work, args)
         del work
         torch.cuda.empty_cache()
         if env.world == 1:
+            extras["lm_head"] = lm_head_leg(env, args)
             extras["decode"] = decode_leg(args)
         else:
             extras["tp"] = {mode: tp_stack(env, args, mode, 64, 4) for mode in ("single", "fused")}

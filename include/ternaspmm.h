@@ -41,6 +41,26 @@ extern "C" {
 typedef void* ternaspmm_stream_t; /* cudaStream_t */
 typedef uint16_t ternaspmm_bf16;  /* bf16 bit pattern */
 
+/* One item of a work list (see ternaspmm_list_plan below). */
+typedef struct {
+    int8_t* x;                   /* int8 [M][K] */
+    uint64_t* bitmap;
+    int* tile_offsets;
+    uint16_t* quarter_offsets;
+    uint32_t* sign_words;
+    ternaspmm_bf16* out;         /* bf16 [M][N] */
+    ternaspmm_bf16* s;           /* bf16 [M] */
+    ternaspmm_bf16* ws;          /* bf16 [4] */
+    ternaspmm_bf16* residual;    /* bf16 [M][N] or null */
+    int ws_num, M, N, K;
+    int seg1, seg2, seg3;        /* explicit scale-segment boundaries; all zero = the reference's rule */
+    int prefill_form;            /* 0 = decode epilogue, 1 = prefill epilogue, -1 = by token count */
+} ternaspmm_list_item;
+
+typedef struct ternaspmm_list ternaspmm_list;
+
+#ifndef TERNASPMM_TYPES_ONLY   /* the library's own translation unit takes the types only */
+
 /* ---- entry points that replace the reference's, same signatures -------- */
 
 /* Replaces bitlinear_TernaSpMM (kernels/TernaSpMM.cu:25-71).  M <= 64 uses
@@ -213,6 +233,28 @@ void ternaspmm_tp_allreduce_finish(float** bufs, unsigned int** flags, ternaspmm
                                    int full_width, int M, int N, ternaspmm_bf16* residual,
                                    ternaspmm_stream_t stream);
 
+/* ---- work lists: many independent small-batch linears in one persistent launch ------------------
+ * One item is what one call of bitlinear_TernaSpMM / ternaspmm_linear_segments /
+ * bitlinear_TernaSpMM_residual computes, for 1 <= M <= 16 tokens.  A list runs all its items in ONE
+ * kernel launch: a CTA per SM stays resident, builds the decode tables once and streams the items'
+ * weights back to back, so the per-call costs (launch, table build, dependency wait, grid drain)
+ * are paid once per list instead of once per linear.  The items must be independent: no item may
+ * read what another item of the same list writes.  Results are bit-identical to the per-call
+ * entry points.  Usage: ternaspmm_list_plan() -> sizes; the caller allocates the device table and
+ * the scratch area; ternaspmm_list_create() uploads the table and zeroes the scratch area
+ * (synchronises the stream; not while capturing); ternaspmm_list_run() launches (no allocation,
+ * no synchronisation: may be captured into a CUDA graph, any number of times);
+ * ternaspmm_list_destroy() frees the host-side handle.  Runs of lists that share a scratch area
+ * must not overlap on the GPU.  If a run ends with status 4, zero the scratch area before reuse. */
+/* Number of device entries the items need (a layer of more than 18944 outputs takes several), or
+ * -1 for a bad item; *table_bytes / *scratch_bytes receive the sizes of the two device buffers. */
+int ternaspmm_list_plan(const ternaspmm_list_item* items, int n_items, long long* table_bytes,
+                        long long* scratch_bytes);
+ternaspmm_list* ternaspmm_list_create(const ternaspmm_list_item* items, int n_items, void* device_table,
+                                      void* scratch, ternaspmm_stream_t stream);
+void ternaspmm_list_run(ternaspmm_list* list, ternaspmm_stream_t stream);
+void ternaspmm_list_destroy(ternaspmm_list* list);
+
 /* Output head for decode-sized batches: logits[t][v] = sum_k h[t][k] * embedding[v][k] for
  * 1 <= M <= 8 rows of hidden states, bf16 inputs, fp32 accumulation, and the greedy token per
  * row, in one launch that reads the embedding once.  Replaces the dense bf16 GEMM over the tied
@@ -247,6 +289,8 @@ int ternaspmm_transcode_reference_layout(const uint64_t* ref_bitmap, const int* 
                                          const uint32_t* ref_sign_words, int N, int K,
                                          uint64_t* out_bitmap, uint16_t* out_quarter_offsets,
                                          uint32_t* out_sign_words);
+
+#endif /* TERNASPMM_TYPES_ONLY */
 
 #ifdef __cplusplus
 }

@@ -11,10 +11,15 @@
 #include <stdlib.h>
 
 #include <algorithm>
+#include <vector>
+
+#define TERNASPMM_TYPES_ONLY   // the item struct of the work lists; the prototypes use plain-C stand-in types
+#include "ternaspmm.h"
 
 #include "act_quant.cuh"
 #include "lm_head.cuh"
 #include "spmm_large_m.cuh"
+#include "spmm_list.cuh"
 #include "spmm_small_m.cuh"
 
 namespace tsp {
@@ -61,9 +66,10 @@ static int device_sm_count() {
 //   TERNASPMM_CLUSTER_COST_X10   small-batch kernel, thin shape: price of a K split in tenths of a tile time
 //   TERNASPMM_LARGE_MIN_M        smallest token count sent to the tcgen05 kernel (default 33)
 //   TERNASPMM_LARGE_SPLIT=0      tcgen05 kernel without its cluster K split
+//   TERNASPMM_LIST_WARPS         work-list kernel at 8 tokens: 20, 24 (default) or 28 warps per CTA
 struct Tuning {
     int ctas_x10 = 0, max_warps = 0, pdl = 1, large_min_m = 33, large_split = 1, cluster_cost_x10 = 0, fat = 1,
-        force_s = 0, force_w = 0, stage = 1, rpc2 = 1;
+        force_s = 0, force_w = 0, stage = 1, rpc2 = 1, list_warps = 24;
     Tuning() {
         if (const char* e = getenv("TERNASPMM_PDL")) pdl = atoi(e) != 0;
 #ifdef TSP_TUNING
@@ -77,6 +83,7 @@ struct Tuning {
         if (const char* e = getenv("TERNASPMM_RPC2")) rpc2 = atoi(e) != 0;
         if (const char* e = getenv("TERNASPMM_FORCE_S")) force_s = atoi(e);
         if (const char* e = getenv("TERNASPMM_FORCE_W")) force_w = atoi(e);
+        if (const char* e = getenv("TERNASPMM_LIST_WARPS")) list_warps = atoi(e);
 #endif
     }
 };
@@ -609,6 +616,169 @@ extern "C" void ternaspmm_tp_allreduce_finish(float** bufs, unsigned int** flags
                            (const __nv_bfloat16*)ws, eps, full_width, M, N, (const __nv_bfloat16*)residual,
                            status, g_wait_limit_ns) != cudaSuccess)
         t_host_status = ST_LAUNCH;
+    checkLastCudaError(__LINE__);
+}
+
+// ---- work lists ----------------------------------------------------------------------------------
+struct ternaspmm_list {
+    void* device_table;
+    void* scratch;
+    int entries, mt, acc_ld;
+};
+
+// Validates the items and turns them into device entries (a layer with more than kListMaxRT row
+// tiles becomes several entries over row ranges).  Returns false on a bad item.
+static bool list_entries(const ternaspmm_list_item* items, int n, std::vector<ListItem>& out, int& max_m, int& acc_ld) {
+    max_m = 0, acc_ld = 0;
+    for (int i = 0; i < n; ++i) {
+        const ternaspmm_list_item& u = items[i];
+        if (u.M < 1 || u.M > 16 || u.N < 64 || u.K < 64 || (u.N % 64) || (u.K % 64) || u.K / 64 > 4095 || u.ws_num < 1 ||
+            u.ws_num > 4) {
+            fprintf(stderr, "ternaspmm: list item %d: unsupported shape M=%d N=%d K=%d ws_num=%d (need 1<=M<=16, N%%64==0, K%%64==0)\n",
+                    i, u.M, u.N, u.K, u.ws_num);
+            t_host_status = ST_BAD_SHAPE;
+            return false;
+        }
+        if (!u.x || !u.bitmap || !u.tile_offsets || !u.quarter_offsets || !u.sign_words || !u.out || !u.s || !u.ws ||
+            (reinterpret_cast<uintptr_t>(u.x) & 15) || (reinterpret_cast<uintptr_t>(u.bitmap) & 15) ||
+            (reinterpret_cast<uintptr_t>(u.sign_words) & 15)) {
+            fprintf(stderr, "ternaspmm: list item %d: null or misaligned pointer\n", i);
+            t_host_status = ST_BAD_POINTER;
+            return false;
+        }
+        const int epi = u.prefill_form < 0 ? (u.M <= 64 ? EPI_DECODE : EPI_PREFILL) : (u.prefill_form ? EPI_PREFILL : EPI_DECODE);
+        ListItem e = {};
+        e.x = u.x, e.tile_off = u.tile_offsets, e.quarter_off = u.quarter_offsets, e.signs = u.sign_words;
+        e.s = reinterpret_cast<const __nv_bfloat16*>(u.s), e.ws = reinterpret_cast<const __nv_bfloat16*>(u.ws);
+        e.M = u.M, e.K = u.K, e.ld_out = u.N, e.layer_n = u.N, e.ws_num = u.ws_num, e.epilogue = epi;
+        if (u.seg1 || u.seg2 || u.seg3) {   // explicit boundaries
+            const int b[3] = {u.seg1, u.seg2, u.seg3};
+            for (int k = 0; k < 3; ++k) e.seg_b[k] = (k + 1 < u.ws_num) ? b[k] : INT_MAX;
+            e.seg_gran = 1;
+        } else {                            // the reference's rules (see ws_group in spmm_small_m.cuh)
+            const bool prefill = epi == EPI_PREFILL;
+            e.seg_gran = prefill ? 128 : 8;
+            if (u.N == 3840 && (prefill || u.ws_num == 3)) {
+                e.seg_b[0] = 2560, e.seg_b[1] = 3200, e.seg_b[2] = INT_MAX;
+            } else {
+                const int gw = u.N / u.ws_num;
+                e.seg_b[0] = gw, e.seg_b[1] = 2 * gw, e.seg_b[2] = 3 * gw;
+            }
+        }
+        // a CTA's chunk of an entry may reach into at most kListSlots row tiles: at most two row tiles per CTA
+        const int RT = u.N / 64, KT = u.K / 64;
+        const int max_rt = std::min(kListMaxRT, 2 * device_sm_count());
+        const int parts = (RT + max_rt - 1) / max_rt;
+        for (int part = 0; part < parts; ++part) {
+            const int rt0 = (int)((long long)RT * part / parts), rt1 = (int)((long long)RT * (part + 1) / parts);
+            ListItem p = e;
+            p.n0 = rt0 * 64, p.N = (rt1 - rt0) * 64;
+            p.bitmap = reinterpret_cast<const uint32_t*>(u.bitmap) + (size_t)rt0 * KT * 128;
+            p.tile_off = u.tile_offsets + (size_t)rt0 * KT;            // the offsets themselves are absolute
+            p.quarter_off = u.quarter_offsets + (size_t)3 * rt0 * KT;
+            p.out = reinterpret_cast<__nv_bfloat16*>(u.out) + p.n0;
+            p.residual = u.residual ? reinterpret_cast<const __nv_bfloat16*>(u.residual) + p.n0 : nullptr;
+            out.push_back(p);
+            acc_ld = std::max(acc_ld, p.N);
+        }
+        max_m = std::max(max_m, u.M);
+    }
+    if ((int)out.size() > kListMaxItems || out.empty()) {
+        fprintf(stderr, "ternaspmm: a list holds 1..%d entries (got %d)\n", kListMaxItems, (int)out.size());
+        t_host_status = ST_BAD_SHAPE;
+        return false;
+    }
+    return true;
+}
+
+extern "C" int ternaspmm_list_plan(const ternaspmm_list_item* items, int n_items, long long* table_bytes,
+                                   long long* scratch_bytes) {
+    t_host_status = ST_OK;
+    std::vector<ListItem> e;
+    int max_m, acc_ld;
+    if (!items || n_items < 1 || !list_entries(items, n_items, e, max_m, acc_ld)) {
+        if (t_host_status == ST_OK) t_host_status = ST_BAD_POINTER;
+        return -1;
+    }
+    if (table_bytes) *table_bytes = (long long)e.size() * sizeof(ListItem);
+    if (scratch_bytes) *scratch_bytes = (long long)sizeof(ListScratch) + (long long)kListRing * 16 * acc_ld * 4;
+    return (int)e.size();
+}
+
+extern "C" ternaspmm_list* ternaspmm_list_create(const ternaspmm_list_item* items, int n_items, void* device_table,
+                                                 void* scratch, cudaStream_t stream) {
+    t_host_status = ST_OK;
+    std::vector<ListItem> e;
+    int max_m, acc_ld;
+    if (!items || n_items < 1 || !device_table || !scratch || (reinterpret_cast<uintptr_t>(device_table) & 15) ||
+        (reinterpret_cast<uintptr_t>(scratch) & 15)) {
+        t_host_status = ST_BAD_POINTER;
+        return nullptr;
+    }
+    if (!list_entries(items, n_items, e, max_m, acc_ld)) return nullptr;
+    const size_t scratch_bytes = sizeof(ListScratch) + (size_t)kListRing * 16 * acc_ld * 4;
+    if (cudaMemcpyAsync(device_table, e.data(), e.size() * sizeof(ListItem), cudaMemcpyHostToDevice, stream) != cudaSuccess ||
+        cudaMemsetAsync(scratch, 0, scratch_bytes, stream) != cudaSuccess || cudaStreamSynchronize(stream) != cudaSuccess) {
+        t_host_status = ST_LAUNCH;
+        return nullptr;
+    }
+    ternaspmm_list* l = static_cast<ternaspmm_list*>(malloc(sizeof(ternaspmm_list)));
+    if (!l) return nullptr;
+    l->device_table = device_table, l->scratch = scratch, l->entries = (int)e.size();
+    l->mt = max_m <= 8 ? 1 : 2, l->acc_ld = acc_ld;
+    return l;
+}
+
+extern "C" void ternaspmm_list_destroy(ternaspmm_list* l) { free(l); }
+
+template <int MT, int W>
+static cudaError_t launch_list(const ternaspmm_list* l, int* status, cudaStream_t stream) {
+    using L = ListSmem<MT>;
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    auto kern = spmm_list_kernel<MT, W>;
+    if (!attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
+        if (e != cudaSuccess) return e;
+        attr_done[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(device_sm_count(), 1, 1);       // one persistent CTA per SM
+    cfg.blockDim = dim3(W * 32, 1, 1);
+    cfg.dynamicSmemBytes = L::total;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tuning().pdl ? 1 : 0;
+    t_echo = {5, MT * 8, 1, W, 0, (int)cfg.gridDim.x};
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<const ListItem*>(l->device_table), l->entries,
+                              static_cast<uint8_t*>(l->scratch), l->acc_ld, status);
+}
+
+extern "C" void ternaspmm_list_run(ternaspmm_list* l, cudaStream_t stream) {
+    t_host_status = ST_OK;
+    if (!l) {
+        t_host_status = ST_BAD_POINTER;
+        return;
+    }
+    int* status = status_device_ptr();
+    if (!status) {
+        t_host_status = ST_LAUNCH;
+        return;
+    }
+    cudaError_t e;
+    if (l->mt == 2) e = launch_list<2, 16>(l, status, stream);
+    else if (tuning().list_warps == 20) e = launch_list<1, 20>(l, status, stream);
+    else if (tuning().list_warps == 28) e = launch_list<1, 28>(l, status, stream);
+    else e = launch_list<1, 24>(l, status, stream);   // 80 registers per thread without spills
+    if (e != cudaSuccess) {
+        fprintf(stderr, "ternaspmm: list launch failed: %s\n", cudaGetErrorString(e));
+        t_host_status = ST_LAUNCH;
+    }
     checkLastCudaError(__LINE__);
 }
 

@@ -21,6 +21,13 @@ _I = ctypes.c_int
 _SPMM_ARGS = [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P]
 
 
+class ListItem(ctypes.Structure):
+    """``ternaspmm_list_item`` of include/ternaspmm.h."""
+    _fields_ = [(n, _P) for n in ("x", "bitmap", "tile_offsets", "quarter_offsets", "sign_words", "out", "s", "ws",
+                                  "residual")] + \
+               [(n, _I) for n in ("ws_num", "M", "N", "K", "seg1", "seg2", "seg3", "prefill_form")]
+
+
 def library_path() -> str:
     return os.path.join(_CSRC, "libternaspmm.so")
 
@@ -64,6 +71,14 @@ def load_library() -> ctypes.CDLL:
     lib.ternaspmm_last_launch_shape.restype = None
     lib.ternaspmm_debug_inject_host_failure.argtypes = [_I]
     lib.ternaspmm_debug_inject_host_failure.restype = None
+    lib.ternaspmm_list_plan.argtypes = [_P, _I, ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_longlong)]
+    lib.ternaspmm_list_plan.restype = _I
+    lib.ternaspmm_list_create.argtypes = [_P, _I, _P, _P, _P]
+    lib.ternaspmm_list_create.restype = _P
+    lib.ternaspmm_list_run.argtypes = [_P, _P]
+    lib.ternaspmm_list_run.restype = None
+    lib.ternaspmm_list_destroy.argtypes = [_P]
+    lib.ternaspmm_list_destroy.restype = None
     lib.ternaspmm_lm_head_argmax.argtypes = [_P, _P, _I, _I, _I, _P, _P, _I, _P, _P]
     lib.ternaspmm_lm_head_argmax.restype = None
     lib.ternaspmm_lm_head_scratch_bytes.argtypes = []
@@ -103,6 +118,7 @@ EXPORTED_SYMBOLS = (
     "bitlinear_TernaSpMM_benchmark", "checkLastCudaError", "reorder_WT_h", "convert_reorderd",
     "gpu_sleep", "ternaspmm_last_status", "ternaspmm_set_wait_limit_ms", "ternaspmm_last_launch_shape",
     "ternaspmm_debug_inject_host_failure", "ternaspmm_lm_head_argmax", "ternaspmm_lm_head_scratch_bytes",
+    "ternaspmm_list_plan", "ternaspmm_list_create", "ternaspmm_list_run", "ternaspmm_list_destroy",
     "ternaspmm_accumulate_i32", "ternaspmm_linear_segments", "bitlinear_TernaSpMM_residual", "ternaspmm_quant",
     "ternaspmm_scale_quant_sumsq", "ternaspmm_partial_f32", "ternaspmm_tp_finish", "ternaspmm_tp_allreduce_finish", "ternaspmm_rmsnorm_quant", "ternaspmm_relu2_gate_rmsnorm_quant", "ternaspmm_pack_i8",
     "ternaspmm_unpack_i8", "ternaspmm_transcode_reference_layout",

@@ -104,11 +104,13 @@ def test_reference_kernel_test_program_unchanged(args):
     assert line and "TotalError: 0.00" in line[0], r.stdout
 
 
-@pytest.mark.parametrize("N,K,p_zero", [(2560, 2560, 0.45), (3840, 2560, 0.45), (256, 6912, 0.45), (128, 640, 0.0),
-                                        (128, 640, 0.9), (64, 448, 1.0)])
-def test_reference_decompress_kernel_restores_the_dense_weight(lib, ref, N, K, p_zero):
-    """Stage 1 of the reference's prefill path (mySpMM_Kernel_bitmap_prefill, split 7 as model.py
-    passes it) on weights packed in the reference layout writes exactly the dense ternary matrix -
+@pytest.mark.parametrize("N,K,p_zero,split", [(2560, 2560, 0.45, 7), (3840, 2560, 0.45, 7), (256, 6912, 0.45, 7),
+                                              (128, 640, 0.0, 5), (128, 640, 0.9, 5), (64, 448, 1.0, 7)])
+def test_reference_decompress_kernel_restores_the_dense_weight(lib, ref, N, K, p_zero, split):
+    """Stage 1 of the reference's prefill path (mySpMM_Kernel_bitmap_prefill; split 7 as model.py
+    passes it where the kernel's own split arithmetic allows it: with K/64 k-blocks the last split
+    gets ceil - padding blocks, which must not be negative, so the 10-block case uses 5)
+    on weights packed in the reference layout writes exactly the dense ternary matrix -
     the operand its int8 GEMM multiplies.  The same dense matrix, packed in the B200 order, gives
     bit-exact int32 accumulators in the tcgen05 kernel, so both prefill paths contract identical
     operands.  (The reference's GEMM + epilogue stage cannot be built: unpinned.)"""
@@ -123,7 +125,7 @@ def test_reference_decompress_kernel_restores_the_dense_weight(lib, ref, N, K, p
     d = [dev(a) for a in (bm, tg, tm, cv)]
     dense = torch.full((N * K,), 0x55, dtype=torch.int8, device="cuda")
     rc = ref.ref_decompress_prefill(d[0].data_ptr(), d[1].data_ptr(), d[2].data_ptr(), d[3].data_ptr(),
-                                    dense.data_ptr(), N, K, 7, 0)
+                                    dense.data_ptr(), N, K, split, 0)
     assert rc == 0
     torch.cuda.synchronize()
     assert (dense.cpu().numpy().reshape(N, K) == w).all()
