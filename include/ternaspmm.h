@@ -246,8 +246,8 @@ void ternaspmm_tp_allreduce_finish(float** bufs, unsigned int** flags, ternaspmm
  * no synchronisation: may be captured into a CUDA graph, any number of times);
  * ternaspmm_list_destroy() frees the host-side handle.  Runs of lists that share a scratch area
  * must not overlap on the GPU.  If a run ends with status 4, zero the scratch area before reuse. */
-/* Number of device entries the items need (a layer of more than 18944 outputs takes several), or
- * -1 for a bad item; *table_bytes / *scratch_bytes receive the sizes of the two device buffers. */
+/* Number of device table entries (= items), or -1 for a bad item or more than 256 items;
+ * *table_bytes / *scratch_bytes receive the sizes of the two device buffers. */
 int ternaspmm_list_plan(const ternaspmm_list_item* items, int n_items, long long* table_bytes,
                         long long* scratch_bytes);
 ternaspmm_list* ternaspmm_list_create(const ternaspmm_list_item* items, int n_items, void* device_table,

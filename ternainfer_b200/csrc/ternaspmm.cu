@@ -66,10 +66,10 @@ static int device_sm_count() {
 //   TERNASPMM_CLUSTER_COST_X10   small-batch kernel, thin shape: price of a K split in tenths of a tile time
 //   TERNASPMM_LARGE_MIN_M        smallest token count sent to the tcgen05 kernel (default 33)
 //   TERNASPMM_LARGE_SPLIT=0      tcgen05 kernel without its cluster K split
-//   TERNASPMM_LIST_WARPS         work-list kernel at 8 tokens: 20, 24 (default) or 28 warps per CTA
+//   TERNASPMM_LIST_WARPS         work-list kernel at 8 tokens: 20 (default), 24 or 28 warps per CTA
 struct Tuning {
     int ctas_x10 = 0, max_warps = 0, pdl = 1, large_min_m = 33, large_split = 1, cluster_cost_x10 = 0, fat = 1,
-        force_s = 0, force_w = 0, stage = 1, rpc2 = 1, list_warps = 24;
+        force_s = 0, force_w = 0, stage = 1, rpc2 = 1, list_warps = 20;
     Tuning() {
         if (const char* e = getenv("TERNASPMM_PDL")) pdl = atoi(e) != 0;
 #ifdef TSP_TUNING
@@ -623,19 +623,26 @@ extern "C" void ternaspmm_tp_allreduce_finish(float** bufs, unsigned int** flags
 struct ternaspmm_list {
     void* device_table;
     void* scratch;
-    int entries, mt, acc_ld;
+    int entries, mt;
 };
 
-// Validates the items and turns them into device entries (a layer with more than kListMaxRT row
-// tiles becomes several entries over row ranges).  Returns false on a bad item.
-static bool list_entries(const ternaspmm_list_item* items, int n, std::vector<ListItem>& out, int& max_m, int& acc_ld) {
-    max_m = 0, acc_ld = 0;
+static size_t list_scratch_bytes() { return sizeof(ListScratch) + (size_t)device_sm_count() * kListAreaInts * 4; }
+
+// Validates the items and turns them into device entries.  Returns false on a bad item.
+static bool list_entries(const ternaspmm_list_item* items, int n, std::vector<ListItem>& out, int& max_m) {
+    max_m = 0;
+    long long tiles = 0;
+    if (n > kListMaxItems) {
+        fprintf(stderr, "ternaspmm: a list holds at most %d items (got %d)\n", kListMaxItems, n);
+        t_host_status = ST_BAD_SHAPE;
+        return false;
+    }
     for (int i = 0; i < n; ++i) {
         const ternaspmm_list_item& u = items[i];
-        if (u.M < 1 || u.M > 16 || u.N < 64 || u.K < 64 || (u.N % 64) || (u.K % 64) || u.K / 64 > 4095 || u.ws_num < 1 ||
-            u.ws_num > 4) {
-            fprintf(stderr, "ternaspmm: list item %d: unsupported shape M=%d N=%d K=%d ws_num=%d (need 1<=M<=16, N%%64==0, K%%64==0)\n",
-                    i, u.M, u.N, u.K, u.ws_num);
+        if (u.M < 1 || u.M > 16 || u.N < 64 || u.K < 64 || (u.N % 64) || (u.K % 64) || u.K / 64 > 4095 || u.N / 64 > 4095 ||
+            u.ws_num < 1 || u.ws_num > 4) {
+            fprintf(stderr, "ternaspmm: list item %d: unsupported shape M=%d N=%d K=%d ws_num=%d (need 1<=M<=16, N%%64==0, "
+                            "K%%64==0, N and K below 262144)\n", i, u.M, u.N, u.K, u.ws_num);
             t_host_status = ST_BAD_SHAPE;
             return false;
         }
@@ -648,9 +655,11 @@ static bool list_entries(const ternaspmm_list_item* items, int n, std::vector<Li
         }
         const int epi = u.prefill_form < 0 ? (u.M <= 64 ? EPI_DECODE : EPI_PREFILL) : (u.prefill_form ? EPI_PREFILL : EPI_DECODE);
         ListItem e = {};
-        e.x = u.x, e.tile_off = u.tile_offsets, e.quarter_off = u.quarter_offsets, e.signs = u.sign_words;
+        e.x = u.x, e.bitmap = reinterpret_cast<const uint32_t*>(u.bitmap), e.tile_off = u.tile_offsets;
+        e.quarter_off = u.quarter_offsets, e.signs = u.sign_words;
+        e.out = reinterpret_cast<__nv_bfloat16*>(u.out), e.residual = reinterpret_cast<const __nv_bfloat16*>(u.residual);
         e.s = reinterpret_cast<const __nv_bfloat16*>(u.s), e.ws = reinterpret_cast<const __nv_bfloat16*>(u.ws);
-        e.M = u.M, e.K = u.K, e.ld_out = u.N, e.layer_n = u.N, e.ws_num = u.ws_num, e.epilogue = epi;
+        e.M = u.M, e.N = u.N, e.K = u.K, e.ld_out = u.N, e.ws_num = u.ws_num, e.epilogue = epi;
         if (u.seg1 || u.seg2 || u.seg3) {   // explicit boundaries
             const int b[3] = {u.seg1, u.seg2, u.seg3};
             for (int k = 0; k < 3; ++k) e.seg_b[k] = (k + 1 < u.ws_num) ? b[k] : INT_MAX;
@@ -665,26 +674,12 @@ static bool list_entries(const ternaspmm_list_item* items, int n, std::vector<Li
                 e.seg_b[0] = gw, e.seg_b[1] = 2 * gw, e.seg_b[2] = 3 * gw;
             }
         }
-        // a CTA's chunk of an entry may reach into at most kListSlots row tiles: at most two row tiles per CTA
-        const int RT = u.N / 64, KT = u.K / 64;
-        const int max_rt = std::min(kListMaxRT, 2 * device_sm_count());
-        const int parts = (RT + max_rt - 1) / max_rt;
-        for (int part = 0; part < parts; ++part) {
-            const int rt0 = (int)((long long)RT * part / parts), rt1 = (int)((long long)RT * (part + 1) / parts);
-            ListItem p = e;
-            p.n0 = rt0 * 64, p.N = (rt1 - rt0) * 64;
-            p.bitmap = reinterpret_cast<const uint32_t*>(u.bitmap) + (size_t)rt0 * KT * 128;
-            p.tile_off = u.tile_offsets + (size_t)rt0 * KT;            // the offsets themselves are absolute
-            p.quarter_off = u.quarter_offsets + (size_t)3 * rt0 * KT;
-            p.out = reinterpret_cast<__nv_bfloat16*>(u.out) + p.n0;
-            p.residual = u.residual ? reinterpret_cast<const __nv_bfloat16*>(u.residual) + p.n0 : nullptr;
-            out.push_back(p);
-            acc_ld = std::max(acc_ld, p.N);
-        }
+        e.tile_base = tiles;
+        tiles += (long long)(u.N / 64) * (u.K / 64);
+        out.push_back(e);
         max_m = std::max(max_m, u.M);
     }
-    if ((int)out.size() > kListMaxItems || out.empty()) {
-        fprintf(stderr, "ternaspmm: a list holds 1..%d entries (got %d)\n", kListMaxItems, (int)out.size());
+    if (tiles / std::max(1, device_sm_count()) > (1ll << 30)) {
         t_host_status = ST_BAD_SHAPE;
         return false;
     }
@@ -695,13 +690,13 @@ extern "C" int ternaspmm_list_plan(const ternaspmm_list_item* items, int n_items
                                    long long* scratch_bytes) {
     t_host_status = ST_OK;
     std::vector<ListItem> e;
-    int max_m, acc_ld;
-    if (!items || n_items < 1 || !list_entries(items, n_items, e, max_m, acc_ld)) {
+    int max_m;
+    if (!items || n_items < 1 || !list_entries(items, n_items, e, max_m)) {
         if (t_host_status == ST_OK) t_host_status = ST_BAD_POINTER;
         return -1;
     }
     if (table_bytes) *table_bytes = (long long)e.size() * sizeof(ListItem);
-    if (scratch_bytes) *scratch_bytes = (long long)sizeof(ListScratch) + (long long)kListRing * 16 * acc_ld * 4;
+    if (scratch_bytes) *scratch_bytes = (long long)list_scratch_bytes();
     return (int)e.size();
 }
 
@@ -709,23 +704,22 @@ extern "C" ternaspmm_list* ternaspmm_list_create(const ternaspmm_list_item* item
                                                  void* scratch, cudaStream_t stream) {
     t_host_status = ST_OK;
     std::vector<ListItem> e;
-    int max_m, acc_ld;
+    int max_m;
     if (!items || n_items < 1 || !device_table || !scratch || (reinterpret_cast<uintptr_t>(device_table) & 15) ||
         (reinterpret_cast<uintptr_t>(scratch) & 15)) {
         t_host_status = ST_BAD_POINTER;
         return nullptr;
     }
-    if (!list_entries(items, n_items, e, max_m, acc_ld)) return nullptr;
-    const size_t scratch_bytes = sizeof(ListScratch) + (size_t)kListRing * 16 * acc_ld * 4;
+    if (!list_entries(items, n_items, e, max_m)) return nullptr;
     if (cudaMemcpyAsync(device_table, e.data(), e.size() * sizeof(ListItem), cudaMemcpyHostToDevice, stream) != cudaSuccess ||
-        cudaMemsetAsync(scratch, 0, scratch_bytes, stream) != cudaSuccess || cudaStreamSynchronize(stream) != cudaSuccess) {
+        cudaMemsetAsync(scratch, 0, list_scratch_bytes(), stream) != cudaSuccess || cudaStreamSynchronize(stream) != cudaSuccess) {
         t_host_status = ST_LAUNCH;
         return nullptr;
     }
     ternaspmm_list* l = static_cast<ternaspmm_list*>(malloc(sizeof(ternaspmm_list)));
     if (!l) return nullptr;
     l->device_table = device_table, l->scratch = scratch, l->entries = (int)e.size();
-    l->mt = max_m <= 8 ? 1 : 2, l->acc_ld = acc_ld;
+    l->mt = max_m <= 8 ? 1 : 2;
     return l;
 }
 
@@ -745,8 +739,8 @@ static cudaError_t launch_list(const ternaspmm_list* l, int* status, cudaStream_
         attr_done[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(device_sm_count(), 1, 1);       // one persistent CTA per SM
-    cfg.blockDim = dim3(W * 32, 1, 1);
+    cfg.gridDim = dim3(std::min(device_sm_count(), kListMaxCtas), 1, 1);       // one persistent CTA per SM
+    cfg.blockDim = dim3(W * 32, 1, 1);                  // W - 1 decoder warps and one epilogue warp
     cfg.dynamicSmemBytes = L::total;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -756,7 +750,7 @@ static cudaError_t launch_list(const ternaspmm_list* l, int* status, cudaStream_
     cfg.numAttrs = tuning().pdl ? 1 : 0;
     t_echo = {5, MT * 8, 1, W, 0, (int)cfg.gridDim.x};
     return cudaLaunchKernelEx(&cfg, kern, static_cast<const ListItem*>(l->device_table), l->entries,
-                              static_cast<uint8_t*>(l->scratch), l->acc_ld, status);
+                              static_cast<uint8_t*>(l->scratch), status);
 }
 
 extern "C" void ternaspmm_list_run(ternaspmm_list* l, cudaStream_t stream) {
@@ -770,11 +764,17 @@ extern "C" void ternaspmm_list_run(ternaspmm_list* l, cudaStream_t stream) {
         t_host_status = ST_LAUNCH;
         return;
     }
+#ifdef TSP_TUNING
+    if (const char* ab = getenv("TERNASPMM_LIST_ABLATE")) {
+        const int v = atoi(ab);
+        cudaMemcpyToSymbol(g_list_ablate, &v, sizeof(int));
+    }
+#endif
     cudaError_t e;
     if (l->mt == 2) e = launch_list<2, 16>(l, status, stream);
-    else if (tuning().list_warps == 20) e = launch_list<1, 20>(l, status, stream);
+    else if (tuning().list_warps == 24) e = launch_list<1, 24>(l, status, stream);
     else if (tuning().list_warps == 28) e = launch_list<1, 28>(l, status, stream);
-    else e = launch_list<1, 24>(l, status, stream);   // 80 registers per thread without spills
+    else e = launch_list<1, 20>(l, status, stream);   // 96 registers per thread, no spills: measured faster than 24 or 28 warps with spills
     if (e != cudaSuccess) {
         fprintf(stderr, "ternaspmm: list launch failed: %s\n", cudaGetErrorString(e));
         t_host_status = ST_LAUNCH;

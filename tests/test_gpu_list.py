@@ -88,8 +88,8 @@ def run_and_check(lib, cases, runs=2):
         assert lib.ternaspmm_last_status() == 0
         for c in cases:
             c.check()
-    # header of the scratch area (abort flag, CTA counter, per-item and per-row-tile counters) is back at zero
-    assert (lst.scratch[:16 + 1024 + 4 * 296 * 4] == 0).all()
+    # the whole scratch area (abort flag, arrival counters, boundary areas) is back at zero
+    assert (lst.scratch == 0).all()
     return lst
 
 
@@ -106,12 +106,21 @@ def test_mixed_items_token_counts_residual_segments_and_tiny_shapes(lib):
     run_and_check(lib, cases).close()
 
 
-def test_a_layer_wider_than_one_entry(lib):
-    """More than 296 row tiles: the host splits the layer into entries over row ranges."""
-    cases = [Case(8, 400 * 64, 128, 2, 30), Case(8, 2560, 2560, 1, 31), Case(3, 640 * 64, 64, 3, 32, residual=True)]
+def test_very_wide_and_very_short_layers(lib):
+    """Hundreds of row tiles with one or two k-tiles each (every CTA's share holds many whole row
+    tiles), next to a deep narrow layer (one row tile spread over many CTAs)."""
+    cases = [Case(8, 400 * 64, 128, 2, 30), Case(8, 2560, 2560, 1, 31), Case(3, 640 * 64, 64, 3, 32, residual=True),
+             Case(8, 64, 28672, 1, 33), Case(5, 128, 8192, 2, 34)]
     lst = run_and_check(lib, cases)
-    assert lst.entries == 2 + 1 + 3
+    assert lst.entries == 5
     lst.close()
+
+
+def test_tiny_lists(lib):
+    """Fewer tiles than SMs: only some CTAs get a share."""
+    run_and_check(lib, [Case(8, 64, 64, 1, 70)]).close()
+    run_and_check(lib, [Case(2, 128, 192, 2, 71), Case(8, 64, 128, 1, 72)]).close()
+    run_and_check(lib, [Case(8, 64, 64 * 200, 1, 73)]).close()
 
 
 def test_sixteen_tokens(lib):
