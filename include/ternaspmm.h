@@ -269,6 +269,21 @@ void ternaspmm_lm_head_argmax(ternaspmm_bf16* h, ternaspmm_bf16* embedding, int 
                               long long* argmax, int round_bf16, void* scratch, ternaspmm_stream_t stream);
 long long ternaspmm_lm_head_scratch_bytes(void);
 
+/* No counterpart in the reference.  ternaspmm_lm_head_argmax for callers that cannot provide
+ * scratch memory - an operator inside a runtime that owns all device memory and forbids
+ * cudaMalloc, a latency-critical loop that must not hit the device-wide synchronisation of an
+ * allocation, code running under stream capture.  Same arguments minus `scratch`: the arg-max
+ * candidates and the arrival counter live in a 16 KB array inside the library image (held by every
+ * GPU that loads the library until the process exits).  Limits: 1 <= M <= 8 rows (what the built-in
+ * area has room for; more is rejected with status 1 and a message), K a multiple of 32 up to 12288,
+ * at most 256 CTAs.  Nothing is allocated or freed, here or in a library routine.  The first call on
+ * a device looks up the array's device address (cudaGetSymbolAddress); make that first call outside
+ * any stream capture.  All calls on a device share the one area: it is cleared where it must start
+ * from zero at the head of every call, and calls that overlap on the GPU (different streams) race. */
+void ternaspmm_lm_head_argmax_noalloc(ternaspmm_bf16* h, ternaspmm_bf16* embedding, int M, int V, int K,
+                                      float* logits, long long* argmax, int round_bf16,
+                                      ternaspmm_stream_t stream);
+
 /* Host packer from int8 ternary [N][K] into caller-provided arrays
  * (bitmap N*K/64, tile_offsets tiles+1, quarter_offsets 3*tiles, sign_words
  * at least N*K/32 + 4 words, zero-filled by the call).  Returns the number of

@@ -831,6 +831,88 @@ extern "C" void ternaspmm_lm_head_argmax(__nv_bfloat16* h, __nv_bfloat16* embedd
     checkLastCudaError(__LINE__);
 }
 
+// ---- output head without any caller-provided scratch memory -------------------------------------
+// Some callers of this library cannot hand it scratch memory at all: an operator plugged into a
+// serving runtime that owns every byte of device memory through its own arena and forbids its
+// operators to call cudaMalloc; a control loop for which the device-wide synchronisation hidden in
+// cudaMalloc / cudaFree is unacceptable; code that runs while a stream is being captured, where an
+// allocation is an error.  For them the arg-max candidates and the arrival counter of the head
+// kernel live in the array below, which is part of the library's image: every GPU that loads the
+// library holds these 16 KB until the process exits.
+constexpr int kHeadStaticCtas = 256;   // candidate slots: the launch uses min(SMs, row groups, this many) CTAs
+static __device__ __align__(256) unsigned char g_head_static_scratch[16 + sizeof(HeadCandidate) * 8 * kHeadStaticCtas];
+
+// Device address of the array above on the current device.  The array's NAME is only a host-side
+// handle here - passing it to a kernel would hand the GPU a host address - so the real address is
+// asked for once per device, with that device current, and the answer is kept.
+static void* head_static_scratch_ptr() {
+    static void* ptrs[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_head_static_scratch) != cudaSuccess || !p) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        ptrs[dev] = p;
+    }
+    return ptrs[dev];
+}
+
+extern "C" void ternaspmm_lm_head_argmax_noalloc(__nv_bfloat16* h, __nv_bfloat16* embedding, int M, int V, int K,
+                                                float* logits, long long* argmax, int round_bf16, cudaStream_t stream) {
+    t_host_status = ST_OK;
+    if (M < 1 || M > 8 || V < 1 || K < 32 || (K % 32) || K > 12288) {
+        fprintf(stderr, "ternaspmm: lm_head_argmax_noalloc: the built-in scratch area holds candidates for at most 8 rows; "
+                        "needs 1 <= M <= 8, V >= 1, K a multiple of 32 up to 12288 (got M=%d V=%d K=%d)\n", M, V, K);
+        t_host_status = ST_BAD_SHAPE;
+        return;
+    }
+    if (!h || !embedding || (!logits && !argmax) || (reinterpret_cast<uintptr_t>(h) & 15) ||
+        (reinterpret_cast<uintptr_t>(embedding) & 15)) {
+        fprintf(stderr, "ternaspmm: lm_head_argmax_noalloc: null or misaligned pointer (h, embedding: 16 bytes)\n");
+        t_host_status = ST_BAD_POINTER;
+        return;
+    }
+    void* scratch = head_static_scratch_ptr();   // the first call on a device looks the address up
+    if (!scratch) {
+        fprintf(stderr, "ternaspmm: lm_head_argmax_noalloc: cannot resolve the built-in scratch area on this device\n");
+        t_host_status = ST_LAUNCH;
+        return;
+    }
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!attr_done[dev]) {
+        if (cudaFuncSetAttribute(lm_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * (12288 * 2 + 64)) != cudaSuccess) {
+            t_host_status = ST_LAUNCH;
+            return;
+        }
+        attr_done[dev] = true;
+    }
+    // every call shares the area and finds the previous call's candidates in it; only the arrival
+    // counter has to start at zero, and it is cleared here rather than trusted
+    if (cudaMemsetAsync(scratch, 0, 16, stream) != cudaSuccess) {
+        t_host_status = ST_LAUNCH;
+        return;
+    }
+    HeadParams p;
+    p.h = h, p.emb = embedding, p.logits = logits, p.argmax = argmax;
+    p.counter = reinterpret_cast<unsigned int*>(scratch);
+    p.cand = reinterpret_cast<HeadCandidate*>(reinterpret_cast<uint8_t*>(scratch) + 16);
+    p.M = M, p.V = V, p.K = K, p.round_bf16 = round_bf16;
+    const int groups = (V + 15) / 16;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(std::min(std::min(device_sm_count(), groups), kHeadStaticCtas), 1, 1);
+    cfg.blockDim = dim3(kHeadWarps * 32, 1, 1);
+    cfg.dynamicSmemBytes = 8 * (K * 2 + 64);
+    cfg.stream = stream;
+    if (cudaLaunchKernelEx(&cfg, lm_head_kernel, p) != cudaSuccess) t_host_status = ST_LAUNCH;
+    checkLastCudaError(__LINE__);
+}
+
 extern "C" void ternaspmm_debug_inject_host_failure(int kind) {
     if (kind == 1) t_inject_encode_failure = 1;
 }

@@ -81,6 +81,8 @@ def load_library() -> ctypes.CDLL:
     lib.ternaspmm_list_destroy.restype = None
     lib.ternaspmm_lm_head_argmax.argtypes = [_P, _P, _I, _I, _I, _P, _P, _I, _P, _P]
     lib.ternaspmm_lm_head_argmax.restype = None
+    lib.ternaspmm_lm_head_argmax_noalloc.argtypes = [_P, _P, _I, _I, _I, _P, _P, _I, _P]
+    lib.ternaspmm_lm_head_argmax_noalloc.restype = None
     lib.ternaspmm_lm_head_scratch_bytes.argtypes = []
     lib.ternaspmm_lm_head_scratch_bytes.restype = ctypes.c_longlong
     lib.ternaspmm_accumulate_i32.argtypes = [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P]
@@ -118,6 +120,7 @@ EXPORTED_SYMBOLS = (
     "bitlinear_TernaSpMM_benchmark", "checkLastCudaError", "reorder_WT_h", "convert_reorderd",
     "gpu_sleep", "ternaspmm_last_status", "ternaspmm_set_wait_limit_ms", "ternaspmm_last_launch_shape",
     "ternaspmm_debug_inject_host_failure", "ternaspmm_lm_head_argmax", "ternaspmm_lm_head_scratch_bytes",
+    "ternaspmm_lm_head_argmax_noalloc",
     "ternaspmm_list_plan", "ternaspmm_list_create", "ternaspmm_list_run", "ternaspmm_list_destroy",
     "ternaspmm_accumulate_i32", "ternaspmm_linear_segments", "bitlinear_TernaSpMM_residual", "ternaspmm_quant",
     "ternaspmm_scale_quant_sumsq", "ternaspmm_partial_f32", "ternaspmm_tp_finish", "ternaspmm_tp_allreduce_finish", "ternaspmm_rmsnorm_quant", "ternaspmm_relu2_gate_rmsnorm_quant", "ternaspmm_pack_i8",
