@@ -278,7 +278,12 @@ class Env:
                 replay()
                 self.stream.synchronize()
                 one = max(time.perf_counter() - t0, 1e-6)
-                for _ in range(min(20000, int(min_load_s / one))):
+                extra = min(20000, int(min_load_s / one))
+                if self.world > 1:   # the same count on every rank: the replayed graph may hold collectives
+                    cnt = torch.tensor([extra], dtype=torch.int64, device=self.device)
+                    self.dist.broadcast(cnt, 0)
+                    extra = int(cnt.item())
+                for _ in range(extra):
                     replay()
             self.barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
