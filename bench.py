@@ -694,6 +694,7 @@ def tp_stack(env, args, mode, M, L):
         sys.path.insert(0, os.path.join(ROOT, "oracle"))
         import ternaspmm_oracle as o
         import c_oracle
+        c_oracle.load().oracle_set_num_threads(max(1, (os.cpu_count() or 1) // world))   # torchrun exports OMP_NUM_THREADS=1
         one = np.full(M, 0x3F80, np.uint16)
         for name, (wd, packed, ws, segs) in dense0.items():
             n, k = wd.shape
@@ -714,6 +715,9 @@ def tp_stack(env, args, mode, M, L):
         if not (got == o.f32_to_bf16_bits(v)).all():
             raise SystemExit("tp bench sanity check failed: sharded QKV output differs from the oracle")
     dense0.clear()
+    # rank 0 has just spent seconds on the host-side check: meet here, or the other ranks' first fused
+    # calls would wait for it on the device beyond the library's bounded-wait limit
+    env.barrier()
 
     def step():
         x = x0
