@@ -54,10 +54,12 @@ constexpr int kLgFirstDecoder = kLgFirstEpi + kLgEpiWarps;
 constexpr int kLgKStep = 128;            // k per pipeline stage = one 128-byte swizzle row
 constexpr int kLgAStage = 128 * 128;     // bytes: 128 rows x 128 k int8
 
-template <int NT>
+// DENSE: the weight operand is a dense int8 matrix W[N][K] in global memory (decompressed beforehand,
+// see dense_prefill.cuh) and arrives by TMA like the activations: no decoder warps, no lookup tables.
+template <int NT, bool DENSE = false>
 struct LargeMSmem {
     static constexpr int stages = NT > 128 ? 3 : 4;
-    static constexpr int threads = (kLgFirstDecoder + 4 * stages) * 32;   // four decoder warps per stage
+    static constexpr int threads = DENSE ? kLgFirstDecoder * 32 : (kLgFirstDecoder + 4 * stages) * 32;   // four decoder warps per stage
     static constexpr int bars = 0;                         // full_a[4] full_b[4] empty[4] acc_full[2] acc_empty[2]
     static constexpr int tmem_slot = 136;
     static constexpr int abort_flag = 140;
@@ -65,7 +67,7 @@ struct LargeMSmem {
     static constexpr int a = (scl + kLgEpiWarps * (NT / 2) * 4 + 1023) / 1024 * 1024;
     static constexpr int b = a + stages * kLgAStage;
     static constexpr int rest = b + stages * NT * kLgKStep;
-    static constexpr int tables = NT <= 64 ? 2 : 1;        // the two-table decode where shared memory allows it
+    static constexpr int tables = DENSE ? 0 : (NT <= 64 ? 2 : 1);   // the two-table decode where shared memory allows it
     static constexpr int total = (tables + 1) * kLutBytes + rest;   // tables aligned to 32 KB, the rest behind them
 };
 
@@ -130,10 +132,11 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     return false;
 }
 
-template <int NT>
-__global__ void __launch_bounds__(LargeMSmem<NT>::threads, 1)
-    spmm_large_m_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap tmap_x) {
-    using L = LargeMSmem<NT>;
+template <int NT, bool DENSE = false>
+__global__ void __launch_bounds__(LargeMSmem<NT, DENSE>::threads, 1)
+    spmm_large_m_kernel(const SpmmParams p, const __grid_constant__ CUtensorMap tmap_x,
+                        const __grid_constant__ CUtensorMap tmap_w) {
+    using L = LargeMSmem<NT, DENSE>;
     constexpr int ST = L::stages;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t dyn = smem_u32(smem);
@@ -171,7 +174,7 @@ __global__ void __launch_bounds__(LargeMSmem<NT>::threads, 1)
     // ---- set-up
     if (tid == 0) {
         for (int s = 0; s < 4; ++s) {
-            mbar_init(bar_full_a(s), 4);   // the four decoder warps of a stage
+            mbar_init(bar_full_a(s), DENSE ? 1 : 4);   // the four decoder warps of a stage (dense: the loader thread + TMA bytes)
             mbar_init(bar_full_b(s), 1);   // the loader thread (+ TMA bytes)
             mbar_init(bar_empty(s), 1);    // tcgen05.commit
         }
@@ -187,6 +190,7 @@ __global__ void __launch_bounds__(LargeMSmem<NT>::threads, 1)
     for (int e = tid; e < 256 * L::tables; e += L::threads) lut1[e] = e < 256 ? lut_entry(e) : lut_entry_upper(e - 256);
     __syncthreads();
     for (int i = tid; i < 256 * 8 * L::tables; i += L::threads) sts128(lut_base + i * 16, make_uint4(lut1[i >> 3], lut1[i >> 3], lut1[i >> 3], lut1[i >> 3]));
+    if (DENSE) griddep_wait();   // the dense weights were written by the previous kernel of the stream
     if (warp == 1) tmem_alloc(sbase + L::tmem_slot, 2 * NT);
     tc_fence_before();
     __syncthreads();
@@ -209,6 +213,10 @@ __global__ void __launch_bounds__(LargeMSmem<NT>::threads, 1)
                     if (!ok) break;
                     mbar_arrive_expect_tx(bar_full_b(s), NT * kLgKStep);
                     tma_load_2d(sbase + L::b + s * (NT * kLgKStep), &tmap_x, ks * kLgKStep, t0, bar_full_b(s));
+                    if (DENSE) {   // 128 weight rows x 128 k of the dense matrix (rows beyond N read as zero)
+                        mbar_arrive_expect_tx(bar_full_a(s), kLgAStage);
+                        tma_load_2d(sbase + L::a + s * kLgAStage, &tmap_w, ks * kLgKStep, (tile % RB) * 128, bar_full_a(s));
+                    }
                 }
             }
         }
@@ -244,7 +252,7 @@ __global__ void __launch_bounds__(LargeMSmem<NT>::threads, 1)
             }
             phase_mark_here(3);
         }
-    } else if (warp >= kLgFirstDecoder) {
+    } else if (!DENSE && warp >= kLgFirstDecoder) {
         // ---------------------------------------------------------- decoders
         const int dw = warp - kLgFirstDecoder;
         const int half = dw & 1, kk = (dw >> 1) & 1, grp = dw >> 2;   // grp = the pipeline stage this group owns

@@ -17,6 +17,7 @@
 #include "ternaspmm.h"
 
 #include "act_quant.cuh"
+#include "dense_prefill.cuh"
 #include "lm_head.cuh"
 #include "spmm_large_m.cuh"
 #include "spmm_list.cuh"
@@ -226,6 +227,7 @@ static cudaError_t launch_small_m(SpmmParams& p, int token_blocks, int warp_slot
 // 128 k, 128-byte swizzle, out-of-range rows and columns read as zero.
 static thread_local int t_inject_encode_failure = 0;   // test hook: the next encode on this thread reports failure
 
+// (also used for the dense weight matrix W[N][K]: rows = N, box = 128 rows)
 static bool encode_x_map(CUtensorMap* map, const void* x, int M, int K, int NT) {
     if (t_inject_encode_failure) {
         t_inject_encode_failure = 0;
@@ -251,23 +253,28 @@ static bool encode_x_map(CUtensorMap* map, const void* x, int M, int K, int NT) 
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int NT>
-static cudaError_t launch_large_m(const SpmmParams& p_in, cudaStream_t stream) {
-    using L = LargeMSmem<NT>;
+template <int NT, bool DENSE = false>
+static cudaError_t launch_large_m(const SpmmParams& p_in, cudaStream_t stream, const int8_t* dense_w = nullptr) {
+    using L = LargeMSmem<NT, DENSE>;
     static bool attr_done[64] = {false};
     static int max_clusters[64][4] = {};   // co-resident clusters of 2 / 4 / 8 CTAs (index log2), 0 = not asked yet
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
-    auto kern = spmm_large_m_kernel<NT>;
+    auto kern = spmm_large_m_kernel<NT, DENSE>;
     if (!attr_done[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total);
         if (e != cudaSuccess) return e;
         attr_done[dev] = true;
     }
     SpmmParams p = p_in;
-    CUtensorMap map;
+    CUtensorMap map, wmap;
     if (!encode_x_map(&map, p.x, p.M, p.K, NT)) return cudaErrorInvalidValue;   // reported as status 3, nothing is launched
+    if (DENSE) {
+        if (!encode_x_map(&wmap, dense_w, p.N, p.K, 128)) return cudaErrorInvalidValue;
+    } else {
+        wmap = map;   // unused by the kernel
+    }
     const long long tiles = (long long)((p.N + 127) / 128) * ((p.M + NT - 1) / NT);
     const int sms = device_sm_count(), KS = (p.K + kLgKStep - 1) / kLgKStep;
     cudaLaunchConfig_t cfg = {};
@@ -286,7 +293,7 @@ static cudaError_t launch_large_m(const SpmmParams& p_in, cudaStream_t stream) {
     // K split over a cluster when the tiles alone would leave more than half of the SMs idle:
     // the largest cluster of 2/4/8 CTAs that still fits the chip in one wave with >= 2 k-steps per CTA.
     p.splits = 1;
-    if (tiles * 2 <= sms && tuning().large_split) {
+    if (!DENSE && tiles * 2 <= sms && tuning().large_split) {   // (the dense variant has no K split: its callers pick shapes that fill the chip)
         for (int lg = 3; lg >= 1; --lg) {
             const int S = 1 << lg;
             if (tiles * S > sms || KS < 2 * S || NT / S < 16) continue;
@@ -309,8 +316,8 @@ static cudaError_t launch_large_m(const SpmmParams& p_in, cudaStream_t stream) {
     attr[0].val.clusterDim.x = p.splits;
     // persistent: one CTA per SM walks over the tiles (with a K split: one tile per cluster)
     cfg.gridDim = dim3(p.splits > 1 ? (unsigned)(tiles * p.splits) : (unsigned)std::min<long long>(tiles, sms), 1, 1);
-    t_echo = {3, NT, p.splits, L::threads / 32, 2, (int)cfg.gridDim.x};
-    return cudaLaunchKernelEx(&cfg, kern, p, map);
+    t_echo = {DENSE ? 6 : 3, NT, p.splits, L::threads / 32, 2, (int)cfg.gridDim.x};
+    return cudaLaunchKernelEx(&cfg, kern, p, map, wmap);
 }
 
 static void run_spmm(int8_t* x, uint64_t* bitmap, int* tile_off, uint16_t* quarter_off, uint32_t* signs, void* out,
@@ -454,6 +461,99 @@ extern "C" void bitlinear_TernaSpMM_residual(int8_t* x, uint64_t* bitmap, int* t
                                             __nv_bfloat16* residual, cudaStream_t stream) {
     run_spmm(x, bitmap, tile_offsets, quarter_offsets, sign_words, out, s, ws, ws_num, M, N, K,
              M <= 64 ? EPI_DECODE : EPI_PREFILL, stream, nullptr, residual);
+    checkLastCudaError(__LINE__);
+}
+
+// Large-batch path through a dense workspace: decompress once, then the tensor-core kernel with both
+// operands by TMA.  Returns false when the shape is one the on-chip path serves better.
+static bool dense_prefill_pays(int M, int N, int K, long long workspace_bytes) {
+    // Measured on the BitNet-2B layers: decoding once into the workspace wins from about 2048 tokens on
+    // (gate-up at 2048 / 4096 tokens: 87 / 157 us against 94 / 181 us on chip); below that the on-chip
+    // kernel re-decodes little and, for narrow layers, fills the chip with its cluster K split.
+    if (workspace_bytes < (long long)N * K || M < 1536) return false;
+    const long long tiles = (long long)((N + 127) / 128) * ((M + 255) / 256);
+    return tiles * 2 >= device_sm_count();
+}
+
+static cudaError_t launch_decompress(const SpmmParams& p, int8_t* dense, cudaStream_t stream) {
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    const int smem_bytes = kLut2Bytes + kLutBytes + 2048 + 256;
+    if (!attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(decompress_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+        if (e != cudaSuccess) return e;
+        attr_done[dev] = true;
+    }
+    const long long tiles = (long long)(p.N / 64) * (p.K / 64);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)std::min<long long>(device_sm_count(), (tiles + kDecompressWarps - 1) / kDecompressWarps), 1, 1);
+    cfg.blockDim = dim3(kDecompressWarps * 32, 1, 1);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tuning().pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, decompress_kernel, p, dense);
+}
+
+extern "C" void bitlinear_TernaSpMM_ws(int8_t* x, uint64_t* bitmap, int* tile_offsets, uint16_t* quarter_offsets,
+                                       uint32_t* sign_words, __nv_bfloat16* out, __nv_bfloat16* s, __nv_bfloat16* ws,
+                                       int ws_num, int M, int N, int K, __nv_bfloat16* residual, void* workspace,
+                                       long long workspace_bytes, int path, cudaStream_t stream) {
+    const int epilogue = M <= 64 ? EPI_DECODE : EPI_PREFILL;
+    const bool dense = path == 2 || (path == 0 && workspace && dense_prefill_pays(M, N, K, workspace_bytes));
+    if (!dense) {
+        run_spmm(x, bitmap, tile_offsets, quarter_offsets, sign_words, out, s, ws, ws_num, M, N, K, epilogue, stream, nullptr,
+                 residual);
+        checkLastCudaError(__LINE__);
+        return;
+    }
+    t_host_status = ST_OK;
+    if (M < 1 || N < 64 || K < 64 || (N % 64) || (K % 64) || ws_num < 1 || ws_num > 4) {
+        fprintf(stderr, "ternaspmm: unsupported shape M=%d N=%d K=%d ws_num=%d\n", M, N, K, ws_num);
+        t_host_status = ST_BAD_SHAPE;
+        return;
+    }
+    if (!x || !bitmap || !tile_offsets || !quarter_offsets || !sign_words || !out || !s || !ws || !workspace ||
+        workspace_bytes < (long long)N * K || (reinterpret_cast<uintptr_t>(x) & 15) ||
+        (reinterpret_cast<uintptr_t>(bitmap) & 15) || (reinterpret_cast<uintptr_t>(sign_words) & 15) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 127)) {
+        fprintf(stderr, "ternaspmm: bitlinear_TernaSpMM_ws: null or misaligned pointer, or a workspace below N*K bytes "
+                        "(workspace: 128-byte aligned)\n");
+        t_host_status = ST_BAD_POINTER;
+        return;
+    }
+    SpmmParams p = {};
+    p.x = x, p.bitmap = reinterpret_cast<const uint32_t*>(bitmap), p.tile_off = tile_offsets, p.quarter_off = quarter_offsets;
+    p.signs = sign_words, p.out = out, p.s = s, p.ws = ws, p.residual = residual;
+    p.ws_num = ws_num, p.M = M, p.N = N, p.K = K, p.epilogue = epilogue, p.splits = 1;
+    {   // the reference's scale-segment rules (see ws_group in spmm_small_m.cuh)
+        const bool prefill = epilogue == EPI_PREFILL;
+        p.seg_gran = prefill ? 128 : 8;
+        if (N == 3840 && (prefill || ws_num == 3)) {
+            p.seg_b[0] = 2560, p.seg_b[1] = 3200, p.seg_b[2] = INT_MAX;
+        } else {
+            const int gw = N / ws_num;
+            p.seg_b[0] = gw, p.seg_b[1] = 2 * gw, p.seg_b[2] = 3 * gw;
+        }
+    }
+    p.status = status_device_ptr();
+    if (!p.status) {
+        t_host_status = ST_LAUNCH;
+        return;
+    }
+    int8_t* dense_w = static_cast<int8_t*>(workspace);
+    cudaError_t e = launch_decompress(p, dense_w, stream);
+    if (e == cudaSuccess)
+        e = M <= 128 ? launch_large_m<128, true>(p, stream, dense_w) : launch_large_m<256, true>(p, stream, dense_w);
+    if (e != cudaSuccess) {
+        fprintf(stderr, "ternaspmm: launch failed: %s\n", cudaGetErrorString(e));
+        t_host_status = ST_LAUNCH;
+    }
     checkLastCudaError(__LINE__);
 }
 

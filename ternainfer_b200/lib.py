@@ -103,6 +103,8 @@ def load_library() -> ctypes.CDLL:
     lib.ternaspmm_tp_finish.restype = None
     lib.ternaspmm_tp_allreduce_finish.argtypes = [_P, _P, _P, _I, _I, _P, _P, ctypes.c_float, _I, _I, _I, _P, _P]
     lib.ternaspmm_tp_allreduce_finish.restype = None
+    lib.bitlinear_TernaSpMM_ws.argtypes = [_P] * 8 + [_I] * 4 + [_P, _P, ctypes.c_longlong, _I, _P]
+    lib.bitlinear_TernaSpMM_ws.restype = None
     lib.bitlinear_TernaSpMM_residual.argtypes = [_P] * 8 + [_I] * 4 + [_P, _P]
     lib.bitlinear_TernaSpMM_residual.restype = None
     lib.ternaspmm_pack_i8.argtypes = [_P, _I, _I, _P, _P, _P, _P]
@@ -122,7 +124,7 @@ EXPORTED_SYMBOLS = (
     "ternaspmm_debug_inject_host_failure", "ternaspmm_lm_head_argmax", "ternaspmm_lm_head_scratch_bytes",
     "ternaspmm_lm_head_argmax_noalloc",
     "ternaspmm_list_plan", "ternaspmm_list_create", "ternaspmm_list_run", "ternaspmm_list_destroy",
-    "ternaspmm_accumulate_i32", "ternaspmm_linear_segments", "bitlinear_TernaSpMM_residual", "ternaspmm_quant",
+    "ternaspmm_accumulate_i32", "ternaspmm_linear_segments", "bitlinear_TernaSpMM_residual", "bitlinear_TernaSpMM_ws", "ternaspmm_quant",
     "ternaspmm_scale_quant_sumsq", "ternaspmm_partial_f32", "ternaspmm_tp_finish", "ternaspmm_tp_allreduce_finish", "ternaspmm_rmsnorm_quant", "ternaspmm_relu2_gate_rmsnorm_quant", "ternaspmm_pack_i8",
     "ternaspmm_unpack_i8", "ternaspmm_transcode_reference_layout",
 )

@@ -21,16 +21,29 @@ from torch import nn
 
 from .lib import load_library
 
-_GLOBAL_WORKSPACE = None
+_GLOBAL_WORKSPACE = {}
+_WORKSPACE_BYTES = 13824 * 2560      # the largest BitNet-2B layer as dense int8, as model.py:34 of the reference sizes it
+
+
+def reserve_workspace(nbytes: int):
+    """Raise the size the shared workspace is created with (call before the first forward; a layer
+    whose dense int8 copy does not fit simply keeps the on-chip decode at every token count)."""
+    global _WORKSPACE_BYTES
+    _WORKSPACE_BYTES = max(_WORKSPACE_BYTES, int(nbytes))
 
 
 def get_global_workspace(device="cuda"):
-    """Kept for drop-in compatibility (model.py:37-42).  The B200 kernels do
-    not use a workspace, so a 16-byte placeholder is returned."""
-    global _GLOBAL_WORKSPACE
-    if _GLOBAL_WORKSPACE is None:
-        _GLOBAL_WORKSPACE = torch.empty(16, dtype=torch.int8, device=device)
-    return _GLOBAL_WORKSPACE
+    """One workspace shared by all layers of a device (model.py:37-42 of the reference).  The
+    reference needs it for its split-K partial sums and, at more than 64 tokens, for the dense int8
+    copy of the weight its prefill GEMM reads.  Here only large-batch calls use it, the same way:
+    the weight is decoded once per call into it and both operands reach the tensor cores by TMA."""
+    dev = torch.device(device)
+    if dev.index is None and dev.type == "cuda":
+        dev = torch.device("cuda", torch.cuda.current_device())
+    ws = _GLOBAL_WORKSPACE.get(dev)
+    if ws is None or ws.numel() < _WORKSPACE_BYTES:
+        ws = _GLOBAL_WORKSPACE[dev] = torch.empty(_WORKSPACE_BYTES, dtype=torch.int8, device=dev)
+    return ws
 
 
 def quant_input(input: torch.Tensor):
@@ -38,6 +51,17 @@ def quant_input(input: torch.Tensor):
     s = 127 / clamp(max|x|, 1e-5); x_q = clamp(round(x*s), -128, 127)."""
     s = 127 / input.abs().max(dim=-1, keepdim=True).values.clamp_(min=1e-5)
     return (input * s).round().clamp(-128, 127).to(torch.int8), s
+
+
+def _builtin_segments(segments, out_features, ws_num):
+    """Whether explicit scale-segment lengths say the same as the reference's built-in rule (equal
+    widths, or 2560/640/640 for 3840 outputs with three scales), which is what the entry points
+    without segment arguments apply."""
+    if segments is None or len(segments) <= 1:
+        return True
+    if ws_num == 3 and out_features == 3840:
+        return list(segments) == [2560, 640, 640]
+    return out_features % ws_num == 0 and all(v == out_features // ws_num for v in segments)
 
 
 _ENTRY = {"auto": "bitlinear_TernaSpMM", "decode": "bitlinear_TernaSpMM_decode",
@@ -112,6 +136,18 @@ def TernaInfer_linear(input, compressed_val, TileOffsets_global, TileOffsets_med
     s = s.contiguous()
     ret = torch.empty((M, out_features), dtype=torch.bfloat16, device=input.device)
     stream = torch.cuda.current_stream()
+    if (workspace is not None and mode == "auto" and M > 64 and _builtin_segments(segments, out_features, ws_num)
+            and workspace.numel() * workspace.element_size() >= out_features * K):
+        # large batch with the reference-sized workspace: decode once into it, both operands by TMA
+        res = None
+        if residual is not None:
+            res = residual.reshape(M, out_features)
+            assert res.is_contiguous() and res.dtype == torch.bfloat16
+        lib.bitlinear_TernaSpMM_ws(x2.data_ptr(), bitmap.data_ptr(), TileOffsets_global.data_ptr(),
+                                   TileOffsets_median.data_ptr(), compressed_val.data_ptr(), ret.data_ptr(), s.data_ptr(),
+                                   ws.data_ptr(), ws_num, M, out_features, K, res.data_ptr() if res is not None else None,
+                                   workspace.data_ptr(), workspace.numel() * workspace.element_size(), 0, stream.cuda_stream)
+        return ret.reshape(*out_shape)
     if segments is not None and len(segments) > 1 and residual is None:
         bounds = [sum(segments[:i + 1]) for i in range(len(segments) - 1)] + [2 ** 31 - 1] * 3
         form = {"auto": -1, "decode": 0, "prefill": 1}[mode]
@@ -179,8 +215,8 @@ class SpBitLinear(nn.Module):
         return TernaInfer_linear(
             input_q,
             self.weight_compressed_val, self.weight_TileOffsets_global, self.weight_TileOffsets_median,
-            self.weight_bitmap, None, s, self.weight_scale, self.ws_num, self.out_features, residual=residual,
-            segments=self.segments)
+            self.weight_bitmap, get_global_workspace(input_q.device), s, self.weight_scale, self.ws_num, self.out_features,
+            residual=residual, segments=self.segments)
 
     def forward(self, input):
         input, s = quant_input(input)
