@@ -570,6 +570,83 @@ def lm_head_leg(env, args):
     return out
 
 
+def prefill_leg(env, args, token_counts=(256, 2048, 4096)):
+    """Large-batch calls on the gate-up layer (13824 x 2560, the largest of the sweep): the tcgen05 kernel that
+    decodes on chip, the path through the reference-sized workspace (decompress once, both operands by TMA) and
+    torch's dense bf16 linear on the de-quantised weight (cuBLAS: the comparator of the reference's own kernel
+    test).  One weight, launched back to back: the 7 MB of compressed weight stay in L2, as in that test."""
+    torch, lib = env.torch, env.lib
+    from ternainfer_b200.convert import compress_weight
+    N, K, ws_num = 13824, 2560, 2
+    g = torch.Generator(device=env.device).manual_seed(args.seed)
+    r = torch.rand((N, K), generator=g, device=env.device)
+    sign = torch.randint(0, 2, (N, K), generator=g, device=env.device, dtype=torch.int8) * 2 - 1
+    w = torch.where(r < P_ZERO, torch.zeros((), dtype=torch.int8, device=env.device), sign)
+    cv, tg, tm, bm = compress_weight(w)
+    wd = w.to(torch.bfloat16)
+    ws = torch.tensor([0.02, 0.03, 0.0, 0.0]).to(torch.bfloat16).to(env.device)
+    work = torch.empty(N * K, dtype=torch.int8, device=env.device)
+    peak_tf = None
+    try:
+        peak_tf = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        pass
+    out = {"layer": "gate-up 13824x2560", "note": "int8 tensor-core ops 2*M*N*K per call; fractions are of the measured "
+           "bf16 cuBLAS burst peak (the int8 peak of the part is nominally twice the bf16 one)"}
+    for M in token_counts:
+        xq = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=env.device)
+        sc = (torch.rand(M, device=env.device) * 50 + 1).to(torch.bfloat16)
+        y = torch.empty((M, N), dtype=torch.bfloat16, device=env.device)
+        xb = xq.to(torch.bfloat16)
+
+        def call(path):
+            lib.bitlinear_TernaSpMM_ws(xq.data_ptr(), bm.data_ptr(), tg.data_ptr(), tm.data_ptr(), cv.data_ptr(), y.data_ptr(),
+                                       sc.data_ptr(), ws.data_ptr(), ws_num, M, N, K, None, work.data_ptr(), N * K, path,
+                                       torch.cuda.current_stream().cuda_stream)
+
+        t_chip = env.time_replays(lambda: call(1), args.steps, args.warmup) / args.steps * 1e3
+        a = y.clone()
+        t_ws = env.time_replays(lambda: call(2), args.steps, args.warmup) / args.steps * 1e3
+        if not torch.equal(a, y):
+            raise SystemExit("bench: the two large-batch paths disagree")
+        t_torch = env.time_replays(lambda: torch.nn.functional.linear(xb, wd), args.steps, args.warmup) / args.steps * 1e3
+        ops = 2.0 * M * N * K
+        best = min(t_chip, t_ws)
+        out[str(M)] = {"on_chip_us": t_chip, "workspace_us": t_ws, "torch_bf16_linear_us": t_torch,
+                       "tensor_TOPs": ops / best / 1e6, "frac_of_measured_bf16_peak": (ops / best / 1e6 / peak_tf) if peak_tf else None,
+                       "speedup_vs_torch_bf16": t_torch / best}
+    del w, wd, work
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_single_leg(args):
+    """--workload list | head | prefill: one leg on its own (short runs for profiling)."""
+    env = Env()
+    if args.workload == "list":
+        work, _ = build_workload(env.torch, args.layers, args.seed + 7919 * env.rank, env.device)
+        res = list_leg(env, work, args.tokens, args)
+        line = {"metric": "ternaspmm_algorithmic_GBps", "value": res["value"], "unit": "GB/s", "n_gpus": env.world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "int8xternary->int32->bf16", "data": "synthetic",
+                "config": dict(sweep_config(args, env.world), entry="ternaspmm_list_run"), "roofline": res["roofline"],
+                "gpu_launches": res["gpu_launches"]}
+    elif args.workload == "head":
+        res = lm_head_leg(env, args)
+        line = {"metric": "lm_head_GBps", "value": res["8"]["GBps"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": res["8"]["us_per_call"] / 1e3, "higher_is_better": True,
+                "config": {"workload": "lm_head_argmax_128256x2560_M8"}, "lm_head": res, "gpu_launches": args.steps}
+    else:
+        res = prefill_leg(env, args, (args.tokens,) if args.tokens > 64 else (2048,))
+        key = [k for k in res if k.isdigit()][0]
+        line = {"metric": "prefill_int8_TOPs", "value": res[key]["tensor_TOPs"], "unit": "TOP/s", "n_gpus": 1,
+                "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
+                "config": {"workload": f"gate_up_13824x2560_M{key}"}, "prefill": res, "gpu_launches": 2 * args.steps}
+    if env.rank == 0:
+        print(json.dumps(line), flush=True)
+    _finish(env.world)
+
+
 def run_gpu_arm(args):
     env = Env()
     torch = env.torch
@@ -597,6 +674,7 @@ def run_gpu_arm(args):
         torch.cuda.empty_cache()
         if env.world == 1:
             extras["lm_head"] = lm_head_leg(env, args)
+            extras["prefill"] = prefill_leg(env, args)
             extras["decode"] = decode_leg(args)
         else:
             extras["tp"] = {mode: tp_stack(env, args, mode, 64, 4) for mode in ("single", "fused")}
@@ -940,7 +1018,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=8)
     ap.add_argument("--layers", type=int, default=30)
     ap.add_argument("--seed", type=int, default=1234)
-    ap.add_argument("--workload", default="sweep", choices=["sweep", "tp", "decode"])
+    ap.add_argument("--workload", default="sweep", choices=["sweep", "tp", "decode", "list", "head", "prefill"])
     ap.add_argument("--unfused", action="store_true", help="decode workload: plain torch glue between the linears")
     ap.add_argument("--tp_mode", default="single", choices=["single", "fused", "exact"])
     ap.add_argument("--no_graph", action="store_true", help="tp workload: launch eagerly instead of replaying a CUDA graph")
@@ -955,6 +1033,8 @@ def main():
         run_tp_arm(args)
     elif args.workload == "decode":
         run_decode_arm(args)
+    elif args.workload in ("list", "head", "prefill"):
+        run_single_leg(args)
     else:
         run_gpu_arm(args)
 
