@@ -58,7 +58,7 @@ constexpr int kLgAStage = 128 * 128;     // bytes: 128 rows x 128 k int8
 // see dense_prefill.cuh) and arrives by TMA like the activations: no decoder warps, no lookup tables.
 template <int NT, bool DENSE = false>
 struct LargeMSmem {
-    static constexpr int stages = NT > 128 ? 3 : 4;
+    static constexpr int stages = (NT > 128 && !DENSE) ? 3 : 4;   // dense: no tables in shared memory, room for a fourth stage
     static constexpr int threads = DENSE ? kLgFirstDecoder * 32 : (kLgFirstDecoder + 4 * stages) * 32;   // four decoder warps per stage
     static constexpr int bars = 0;                         // full_a[4] full_b[4] empty[4] acc_full[2] acc_empty[2]
     static constexpr int tmem_slot = 136;
@@ -68,7 +68,8 @@ struct LargeMSmem {
     static constexpr int b = a + stages * kLgAStage;
     static constexpr int rest = b + stages * NT * kLgKStep;
     static constexpr int tables = DENSE ? 0 : (NT <= 64 ? 2 : 1);   // the two-table decode where shared memory allows it
-    static constexpr int total = (tables + 1) * kLutBytes + rest;   // tables aligned to 32 KB, the rest behind them
+    static constexpr int align = DENSE ? 1024 : kLutBytes;          // the stage buffers need 1024 bytes, the tables 32 KB
+    static constexpr int total = tables * kLutBytes + align + rest;   // tables first (aligned), the rest behind them
 };
 
 // ---- tcgen05 wrappers ------------------------------------------------------
@@ -140,8 +141,8 @@ __global__ void __launch_bounds__(LargeMSmem<NT, DENSE>::threads, 1)
     constexpr int ST = L::stages;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t dyn = smem_u32(smem);
-    const uint32_t lut_base = (dyn + (uint32_t)kLutBytes - 1u) & ~((uint32_t)kLutBytes - 1u);
-    const uint32_t sbase = lut_base + L::tables * kLutBytes;  // 32 KB aligned, so the stage buffers are 1024-byte aligned
+    const uint32_t lut_base = (dyn + (uint32_t)L::align - 1u) & ~((uint32_t)L::align - 1u);
+    const uint32_t sbase = lut_base + L::tables * kLutBytes;  // the stage buffers are 1024-byte aligned
     uint8_t* rest = smem + (sbase - dyn);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(rest + L::abort_flag);
     float* s_s = reinterpret_cast<float*>(rest + L::scl);
