@@ -959,7 +959,11 @@ def decode_run(args, bsz, fused, reps):
 def decode_leg(args):
     """Decode tokens/s of the 30-layer model (prompt 512, 128 generated tokens) at batch 1 and 8, with
     the fused front-ends and with plain torch glue between the linears, plus the PyTorch-CPU decode step."""
-    out = {"layers": args.layers, "prompt": 512, "generate": 128}
+    out = {"layers": args.layers, "prompt": 512, "generate": 128,
+           "note": "random-init weights give near-tied logits over 128256 words, so the two glue variants (another "
+                   "fp32 summation order in RMSNorm, another attention kernel) choose different tokens; with the norm's "
+                   "summation order held equal the fused path returns the eager model's logits and tokens exactly "
+                   "(tests/test_gpu_model.py, 30 layers, batch 1 and 8)"}
     for bsz in (1, 8):
         entry = {}
         for fused in (True, False):
