@@ -145,7 +145,7 @@ void ternaspmm_set_wait_limit_ms(int ms);
 /* Test hook: shape of the most recent kernel launch made by this thread.
  * out6 = {kernel (1 = small-batch kernel, one fat CTA per SM; 2 = small-batch
  * kernel, thin CTAs; 3 = tcgen05 kernel; 4 = output head; 5 = work list; 6 = tcgen05 kernel
- * on dense weights from the workspace), tokens per pass, K split (cluster
+ * on dense weights from the workspace, single CTAs; 7 = the same on CTA pairs), tokens per pass, K split (cluster
  * size), warps per CTA, 64-row tiles per CTA, CTAs}. */
 void ternaspmm_last_launch_shape(int* out6);
 

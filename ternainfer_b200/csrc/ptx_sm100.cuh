@@ -72,6 +72,32 @@ __device__ __forceinline__ uint4 ld_cg_128(const void* p) {
     asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
+// Stores and loads that name the global state space.  A store through a generic pointer may alias
+// shared memory as far as the hardware knows, so every later shared-memory load of the warp waits for
+// it; with st.global an epilogue's stores and its next shared-memory reads overlap.
+__device__ __forceinline__ void stg_b16(void* p, unsigned short v) {
+    asm volatile("st.global.b16 [%0], %1;" ::"l"(__cvta_generic_to_global(p)), "h"(v) : "memory");
+}
+__device__ __forceinline__ void stg_b32(void* p, uint32_t v) {
+    asm volatile("st.global.b32 [%0], %1;" ::"l"(__cvta_generic_to_global(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void stg_128(void* p, uint4 v) {
+    asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(__cvta_generic_to_global(p)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ uint4 ldg_128(const void* p) {   // coherent
+    uint4 v;
+    asm volatile("ld.global.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(__cvta_generic_to_global(p)) : "memory");
+    return v;
+}
+__device__ __forceinline__ void sts_b16(uint32_t addr, unsigned short v) {
+    asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(v) : "memory");
+}
+__device__ __forceinline__ unsigned short ldg_b16(const void* p) {   // coherent (the address may be written by this kernel)
+    unsigned short v;
+    asm volatile("ld.global.b16 %0, [%1];" : "=h"(v) : "l"(__cvta_generic_to_global(p)) : "memory");
+    return v;
+}
 __device__ __forceinline__ unsigned long long global_timer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

@@ -53,6 +53,7 @@ constexpr int kLgFirstEpi = 2;           // warp 0 loads activations, warp 1 iss
 constexpr int kLgFirstDecoder = kLgFirstEpi + kLgEpiWarps;
 constexpr int kLgKStep = 128;            // k per pipeline stage = one 128-byte swizzle row
 constexpr int kLgAStage = 128 * 128;     // bytes: 128 rows x 128 k int8
+constexpr int kOutStageBytes = 16 * 32 * 2;   // output staging per epilogue warp
 
 // DENSE: the weight operand is a dense int8 matrix W[N][K] in global memory (decompressed beforehand,
 // see dense_prefill.cuh) and arrives by TMA like the activations: no decoder warps, no lookup tables.
@@ -64,7 +65,8 @@ struct LargeMSmem {
     static constexpr int tmem_slot = 136;
     static constexpr int abort_flag = 140;
     static constexpr int scl = 256;                        // float s[NT / 2] per epilogue warp
-    static constexpr int a = (scl + kLgEpiWarps * (NT / 2) * 4 + 1023) / 1024 * 1024;
+    static constexpr int ostage = scl + kLgEpiWarps * (NT / 2) * 4;   // 1 KB per epilogue warp: a slice of 16 tokens x 32 columns, bf16
+    static constexpr int a = (ostage + kLgEpiWarps * kOutStageBytes + 1023) / 1024 * 1024;
     static constexpr int b = a + stages * kLgAStage;
     static constexpr int rest = b + stages * NT * kLgKStep;
     static constexpr int tables = DENSE ? 0 : (NT <= 64 ? 2 : 1);   // the two-table decode where shared memory allows it
@@ -131,6 +133,100 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     }
     *abort_flag = 1;
     return false;
+}
+// The same for the single threads on the critical path (operand loader, MMA issuer): no sleep between
+// the polls - mbarrier.try_wait suspends the thread in hardware and wakes it when the phase completes,
+// whereas a sleeping thread notices the completion only when its timer runs out.
+__device__ __forceinline__ bool wait_or_abort_hot(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t it = 0; it < (1u << 24); ++it) {
+        if (mbar_test(bar, parity)) return true;
+        if ((it & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+// Epilogue of one 16-token slice of one output column: v = the 16 accumulators, sc = the tokens' scales
+// (or prefill coefficients ws/s), o0 = index of the first output element, live = tokens to store.
+// All loads (residual) are issued before the first store.
+__device__ __forceinline__ void store_slice16(const SpmmParams& p, const int (&v)[16], const float (&sc)[16],
+                                              long long o0, int live, bool fast, float ws_el) {
+    const int N = p.N;
+    if (p.epilogue == EPI_RAW_I32) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (j < live) stg_b32(reinterpret_cast<int*>(p.out) + o0 + (long long)j * N, (uint32_t)v[j]);
+    } else if (p.epilogue == EPI_F32_DIV) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (j < live)
+                stg_b32(reinterpret_cast<float*>(p.out) + o0 + (long long)j * N, __float_as_uint(__fdiv_rn(__int2float_rn(v[j]), sc[j])));
+    } else {
+        __nv_bfloat16 r[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            r[j] = fast ? __float2bfloat16_rn(__fmul_rn(__int2float_rn(v[j]), sc[j]))
+                        : scale_epilogue(v[j], sc[j], ws_el, p.epilogue);
+        if (p.residual) {
+            __nv_bfloat16 res[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) res[j] = j < live ? __ushort_as_bfloat16(ldg_b16(p.residual + o0 + (long long)j * N)) : r[j];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = __float2bfloat16_rn(__bfloat162float(res[j]) + __bfloat162float(r[j]));
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (j < live) stg_b16(reinterpret_cast<__nv_bfloat16*>(p.out) + o0 + (long long)j * N, __bfloat16_as_ushort(r[j]));
+    }
+}
+
+// The bf16 epilogues of a 16-token slice with wide stores.  A lane holds 16 tokens of ONE output column,
+// but the output is [token][column]: stored straight from registers a warp instruction covers 64 bytes,
+// and the store path is bound by the number of such requests (measured: 28 M two-byte stores took longer
+// than the whole contraction).  So the warp transposes the slice through 1 KB of shared memory -
+// [16 tokens][32 columns] - and stores 16 bytes per lane: two instructions of 8 rows x 64 bytes instead of
+// sixteen of one row.  The residual, if any, is read the same way (16 bytes per lane) and added after the
+// first rounding, as in add_residual().  `o_row0` = index of (first token, the warp's first column);
+// needs a 16-byte aligned output (and residual).
+__device__ __forceinline__ void store_slice16_wide(const SpmmParams& p, const int (&v)[16], const float* sc,
+                                                   long long o_row0, int live, bool fast, float ws_el, uint32_t stage,
+                                                   int lane) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const float scj = sc[j];   // the tokens' scales (or prefill coefficients), in shared memory
+        const __nv_bfloat16 r = fast ? __float2bfloat16_rn(__fmul_rn(__int2float_rn(v[j]), scj))
+                                     : scale_epilogue(v[j], scj, ws_el, p.epilogue);
+        sts_b16(stage + (uint32_t)(j * 64 + lane * 2), __bfloat16_as_ushort(r));
+    }
+    __syncwarp();
+    const int part = lane & 3;
+    uint4 d[2], res[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int row = (lane >> 2) + 8 * i;
+        d[i] = lds128(stage + (uint32_t)(row * 64 + part * 16));
+        if (p.residual && row < live) res[i] = ldg_128(p.residual + o_row0 + (long long)row * p.N + part * 8);
+    }
+    if (p.residual) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            uint32_t* dv = reinterpret_cast<uint32_t*>(&d[i]);
+            const uint32_t* rv = reinterpret_cast<const uint32_t*>(&res[i]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float lo = __uint_as_float(rv[e] << 16) + __uint_as_float(dv[e] << 16);
+                const float hi = __uint_as_float(rv[e] & 0xFFFF0000u) + __uint_as_float(dv[e] & 0xFFFF0000u);
+                dv[e] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(lo)) |
+                        ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(hi)) << 16);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int row = (lane >> 2) + 8 * i;
+        if (row < live) stg_128(reinterpret_cast<__nv_bfloat16*>(p.out) + o_row0 + (long long)row * p.N + part * 8, d[i]);
+    }
+    __syncwarp();   // the staging area is free for the next slice
 }
 
 template <int NT, bool DENSE = false>
@@ -322,6 +418,9 @@ __global__ void __launch_bounds__(LargeMSmem<NT, DENSE>::threads, 1)
         constexpr int CW = NT / 2;             // token columns per epilogue warp
         const int cb = ((warp - kLgFirstEpi) >> 2) * CW;
         float* s_w = s_s + (warp - kLgFirstEpi) * CW;   // this warp's scales (or coefficients) of the tile
+        const uint32_t ostage = sbase + L::ostage + (uint32_t)((warp - kLgFirstEpi) * kOutStageBytes);
+        const bool wide = (p.epilogue == EPI_DECODE || p.epilogue == EPI_PREFILL) &&
+                          ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.residual)) & 15) == 0;
         for (int ti = 0; ti < (S == 1 ? my_tiles : 0); ++ti) {
             const int tile = cid + ti * ncl;
             const int rb = tile % RB, t0 = (tile / RB) * NT + cb;
@@ -355,36 +454,16 @@ __global__ void __launch_bounds__(LargeMSmem<NT, DENSE>::threads, 1)
                 // its first store: the output pointer is generic, so a store in between would order
                 // every later load behind it and serialise the slice.
                 int v[16];
-                float sc[16];
                 tmem_ld16(tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)(buf * NT + cb + c0), v);
-#pragma unroll
-                for (int j = 0; j < 16; ++j) sc[j] = s_w[c0 + j];
                 const long long o0 = (long long)(t0 + c0) * N + n;
-                const int live = n_ok ? min(16, M - t0 - c0) : 0;
-                if (p.epilogue == EPI_RAW_I32) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (j < live) reinterpret_cast<int*>(p.out)[o0 + (long long)j * N] = v[j];
-                } else if (p.epilogue == EPI_F32_DIV) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (j < live) reinterpret_cast<float*>(p.out)[o0 + (long long)j * N] = __fdiv_rn(__int2float_rn(v[j]), sc[j]);
+                const int live = n_ok ? min(16, M - t0 - c0) : 0;   // (n_ok is uniform over the warp: N is a multiple of 64)
+                if (wide) {
+                    store_slice16_wide(p, v, s_w + c0, o0 - lane, live, fast, ws_el, ostage, lane);
                 } else {
-                    __nv_bfloat16 r[16];
+                    float sc[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        r[j] = fast ? __float2bfloat16_rn(__fmul_rn(__int2float_rn(v[j]), sc[j]))
-                                    : scale_epilogue(v[j], sc[j], ws_el, p.epilogue);
-                    if (p.residual) {
-                        __nv_bfloat16 res[16];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) res[j] = j < live ? p.residual[o0 + (long long)j * N] : r[j];
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) r[j] = __float2bfloat16_rn(__bfloat162float(res[j]) + __bfloat162float(r[j]));
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (j < live) reinterpret_cast<__nv_bfloat16*>(p.out)[o0 + (long long)j * N] = r[j];
+                    for (int j = 0; j < 16; ++j) sc[j] = s_w[c0 + j];
+                    store_slice16(p, v, sc, o0, live, fast, ws_el);
                 }
             }
             tc_fence_before();
@@ -481,20 +560,21 @@ __global__ void __launch_bounds__(LargeMSmem<NT, DENSE>::threads, 1)
                     for (int j = 0; j < 8; ++j) {
                         const bool live = h + j < ncol;
                         sc[j] = (live && p.epilogue != EPI_RAW_I32) ? s_w[cc0 + h + j] : 1.f;
-                        res[j] = (live && n_ok && p.residual) ? p.residual[(long long)(tb + cc0 + h + j) * N + n]
+                        res[j] = (live && n_ok && p.residual) ? __ushort_as_bfloat16(ldg_b16(p.residual + (long long)(tb + cc0 + h + j) * N + n))
                                                               : __float2bfloat16_rn(0.f);
                     }
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         if (h + j < ncol && n_ok) {
                             const long long o = (long long)(tb + cc0 + h + j) * N + n;
-                            if (p.epilogue == EPI_RAW_I32) reinterpret_cast<int*>(p.out)[o] = v[h + j];
-                            else if (p.epilogue == EPI_F32_DIV) reinterpret_cast<float*>(p.out)[o] = __fdiv_rn(__int2float_rn(v[h + j]), sc[j]);
+                            if (p.epilogue == EPI_RAW_I32) stg_b32(reinterpret_cast<int*>(p.out) + o, (uint32_t)v[h + j]);
+                            else if (p.epilogue == EPI_F32_DIV)
+                                stg_b32(reinterpret_cast<float*>(p.out) + o, __float_as_uint(__fdiv_rn(__int2float_rn(v[h + j]), sc[j])));
                             else {
                                 __nv_bfloat16 r = fast ? __float2bfloat16_rn(__fmul_rn(__int2float_rn(v[h + j]), sc[j]))
                                                        : scale_epilogue(v[h + j], sc[j], ws_el, p.epilogue);
                                 if (p.residual) r = __float2bfloat16_rn(__bfloat162float(res[j]) + __bfloat162float(r));
-                                reinterpret_cast<__nv_bfloat16*>(p.out)[o] = r;
+                                stg_b16(reinterpret_cast<__nv_bfloat16*>(p.out) + o, __bfloat16_as_ushort(r));
                             }
                         }
                     }

@@ -17,6 +17,7 @@
 #include "ternaspmm.h"
 
 #include "act_quant.cuh"
+#include "dense_pair.cuh"
 #include "dense_prefill.cuh"
 #include "lm_head.cuh"
 #include "spmm_large_m.cuh"
@@ -320,6 +321,43 @@ static cudaError_t launch_large_m(const SpmmParams& p_in, cudaStream_t stream, c
     return cudaLaunchKernelEx(&cfg, kern, p, map, wmap);
 }
 
+// Dense tcgen05 GEMM on CTA pairs (dense_pair.cuh): 256 weight rows x 256 tokens per cluster of two CTAs.
+static cudaError_t launch_dense_pair(const SpmmParams& p_in, cudaStream_t stream, const int8_t* dense_w) {
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    auto kern = spmm_dense_pair_kernel;
+    if (!attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::total);
+        if (e != cudaSuccess) return e;
+        attr_done[dev] = true;
+    }
+    SpmmParams p = p_in;
+    p.splits = 1;
+    CUtensorMap map, wmap;   // each CTA of a pair loads 128 tokens and 128 weight rows per stage
+    if (!encode_x_map(&map, p.x, p.M, p.K, 128) || !encode_x_map(&wmap, dense_w, p.N, p.K, 128))
+        return cudaErrorInvalidValue;   // reported as status 3, nothing is launched
+    const long long tiles = (long long)((p.N + kPairRows - 1) / kPairRows) * ((p.M + kPairNT - 1) / kPairNT);
+    const int pairs = (int)std::min<long long>(tiles, device_sm_count() / 2);
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(PairSmem::threads, 1, 1);
+    cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+    cfg.dynamicSmemBytes = PairSmem::total;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tuning().pdl ? 2 : 1;
+    t_echo = {7, kPairNT, 2, PairSmem::threads / 32, 4, (int)cfg.gridDim.x};
+    return cudaLaunchKernelEx(&cfg, kern, p, map, wmap);
+}
+
 static void run_spmm(int8_t* x, uint64_t* bitmap, int* tile_off, uint16_t* quarter_off, uint32_t* signs, void* out,
                      __nv_bfloat16* s, __nv_bfloat16* ws, int ws_num, int M, int N, int K, int epilogue,
                      cudaStream_t stream, const int* seg_bounds = nullptr, const __nv_bfloat16* residual = nullptr) {
@@ -547,9 +585,20 @@ extern "C" void bitlinear_TernaSpMM_ws(int8_t* x, uint64_t* bitmap, int* tile_of
         return;
     }
     int8_t* dense_w = static_cast<int8_t*>(workspace);
-    cudaError_t e = launch_decompress(p, dense_w, stream);
+    cudaError_t e = cudaSuccess;
+#ifdef TSP_TUNING
+    static const int tune_nt = getenv("TERNASPMM_DENSE_NT") ? atoi(getenv("TERNASPMM_DENSE_NT")) : 0;
+    static const int tune_skip = getenv("TERNASPMM_DENSE_SKIP_DECOMPRESS") ? atoi(getenv("TERNASPMM_DENSE_SKIP_DECOMPRESS")) : 0;
+    if (!tune_skip) e = launch_decompress(p, dense_w, stream);
+    static const int tune_pair = getenv("TERNASPMM_DENSE_PAIR") ? atoi(getenv("TERNASPMM_DENSE_PAIR")) : 1;
     if (e == cudaSuccess)
-        e = M <= 128 ? launch_large_m<128, true>(p, stream, dense_w) : launch_large_m<256, true>(p, stream, dense_w);
+        e = (M <= 128 || tune_nt == 128) ? launch_large_m<128, true>(p, stream, dense_w)
+            : (tune_pair ? launch_dense_pair(p, stream, dense_w) : launch_large_m<256, true>(p, stream, dense_w));
+#else
+    e = launch_decompress(p, dense_w, stream);
+    if (e == cudaSuccess)
+        e = M <= 128 ? launch_large_m<128, true>(p, stream, dense_w) : launch_dense_pair(p, stream, dense_w);
+#endif
     if (e != cudaSuccess) {
         fprintf(stderr, "ternaspmm: launch failed: %s\n", cudaGetErrorString(e));
         t_host_status = ST_LAUNCH;

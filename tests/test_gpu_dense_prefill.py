@@ -1,6 +1,6 @@
 """GPU: the large-batch path through a dense workspace (bitlinear_TernaSpMM_ws): the weight is decoded
-once per call into a caller-provided N*K-byte workspace and the tcgen05 kernel takes both operands by
-TMA.  Integer contraction and the same epilogue code as the on-chip path: outputs must equal the CPU
+once per call into a caller-provided N*K-byte workspace and a tcgen05 kernel takes both operands by
+TMA - on CTA pairs (256 x 256 tiles, launch kind 7) above 128 tokens, on single CTAs (kind 6) up to 128.  Integer contraction and the same epilogue code as the on-chip path: outputs must equal the CPU
 oracle bit for bit, and the workspace must hold exactly the dense ternary matrix afterwards."""
 import ctypes
 
@@ -46,10 +46,11 @@ def run_ws(lib, M, N, K, ws_num, path, seed, residual=False, slack=0):
 
 
 @pytest.mark.parametrize("M,N,K,ws_num", [(2048, 13824, 2560, 2), (256, 13824, 2560, 2), (512, 3840, 2560, 3),
-                                          (1000, 2560, 6912, 1), (130, 13824, 2560, 2), (300, 9536, 192, 2)])
+                                          (1000, 2560, 6912, 1), (130, 13824, 2560, 2), (300, 9536, 192, 2),
+                                          (128, 3840, 2560, 3), (4096, 2560, 2560, 1), (2049, 9472, 320, 2)])
 def test_layer_shapes_through_the_workspace(lib, M, N, K, ws_num):
     kind, wk, w = run_ws(lib, M, N, K, ws_num, path=2, seed=M + N)
-    assert kind == 6
+    assert kind == (7 if M > 128 else 6)
     assert (wk[:N * K].reshape(N, K) == w).all(), "the workspace does not hold the dense weight"
     assert (wk[N * K:] == 0x55).all(), "wrote past N*K bytes of the workspace"
 
@@ -58,13 +59,13 @@ def test_layer_shapes_through_the_workspace(lib, M, N, K, ws_num):
 def test_small_and_ragged_shapes_forced_through_the_workspace(lib, M, N, K):
     """A last row block of 64 rows, fewer k than one pipeline step, ragged token tiles, residual."""
     kind, wk, w = run_ws(lib, M, N, K, 2, path=2, seed=M + N + K, residual=True)
-    assert kind == 6
+    assert kind == (7 if M > 128 else 6)
     assert (wk[:N * K].reshape(N, K) == w).all()
 
 
 def test_auto_choice_and_fallbacks(lib):
     kind, _, _ = run_ws(lib, 2048, 13824, 2560, 2, path=0, seed=1)           # big: through the workspace
-    assert kind == 6
+    assert kind == 7
     kind, wk, _ = run_ws(lib, 256, 2560, 2560, 1, path=0, seed=2)            # few output tiles: on chip (cluster K split)
     assert kind == 3 and (wk == 0x55).all()
     kind, wk, _ = run_ws(lib, 64, 13824, 2560, 2, path=0, seed=3)            # decode-sized: never
@@ -107,7 +108,7 @@ def test_python_call_site_uses_the_workspace_at_prefill(lib):
     y = layer(x)
     shape = (ctypes.c_int * 6)()
     lib.ternaspmm_last_launch_shape(shape)
-    assert shape[0] == 6
+    assert shape[0] == 7
     xq, s = o.quant_input(x.float().cpu().numpy())
     _, want = c_oracle.ternaspmm(xq, w, o.f32_to_bf16_bits(s.reshape(-1)), o.f32_to_bf16_bits(wsv), 2, -1)
     assert (y.view(torch.int16).cpu().numpy().view(np.uint16) == want).all()
