@@ -14,10 +14,10 @@
 // memory (32 KB per 128 k) and the accumulators of its 128 weight rows x 256 tokens in its tensor
 // memory - two thirds of the bytes per operation.
 //
-// Roles per CTA (10 warps): warp 0 - one thread issues this CTA's two TMA loads per stage (no
+// Roles per CTA (18 warps): warp 0 - one thread issues this CTA's two TMA loads per stage (no
 // multicast), completing on the LEADER's (cluster rank 0) full barrier; warp 1 - allocates tensor
 // memory (both CTAs), and in the leader one thread issues the MMAs for the pair and commits stage
-// releases / accumulator-complete signals to both CTAs; warps 2-9 - epilogue of this CTA's 128
+// releases / accumulator-complete signals to both CTAs; warps 2-17 - epilogue of this CTA's 128
 // weight rows, handing the accumulator buffer back to the leader's MMA thread.  Six stages, two
 // accumulator buffers of 256 columns.  Every wait is bounded (status 4).
 #pragma once
@@ -29,6 +29,8 @@ constexpr int kPairNT = 256;                 // tokens per tile (the MMA's N)
 constexpr int kPairRows = 256;               // weight rows per tile (the MMA's M over both CTAs)
 constexpr int kPairStages = 6;
 constexpr int kPairHalf = 128 * kLgKStep;    // bytes of one operand half per stage: 128 rows x 128 k
+constexpr int kPairEpiWarps = 16;            // four per 32-lane quarter of tensor memory, a quarter of the token columns each:
+                                             // the epilogue of a slice is a chain of latencies, so more warps hide more of it
 
 #ifdef TSP_PAIR_ABLATE   // tuning builds, compile-time: 1 = no epilogue work, 2 = no weight loads, 4 = no activation loads, 8 = no MMAs
 #define PAIR_ABLATE(bit) ((TSP_PAIR_ABLATE) & (bit))
@@ -37,16 +39,16 @@ constexpr int kPairHalf = 128 * kLgKStep;    // bytes of one operand half per st
 #endif
 
 struct PairSmem {
-    static constexpr int threads = kLgFirstDecoder * 32;
+    static constexpr int threads = (kLgFirstEpi + kPairEpiWarps) * 32;
     static constexpr int bar_full = 0;       // [6]   leader: both CTAs' TMA bytes of a stage have landed
     static constexpr int bar_empty = 48;     // [6]   each CTA: the MMAs have read the stage
     static constexpr int bar_acc_full = 96;  // [2]   each CTA: a tile's accumulators are complete
     static constexpr int bar_acc_empty = 112;   // [2] leader: both CTAs' epilogues have read the buffer
     static constexpr int tmem_slot = 136;
     static constexpr int abort_flag = 140;
-    static constexpr int scl = 256;          // float[128] per epilogue warp
-    static constexpr int ostage = scl + kLgEpiWarps * (kPairNT / 2) * 4;   // 1 KB per epilogue warp (output staging)
-    static constexpr int a = (ostage + kLgEpiWarps * kOutStageBytes + 1023) / 1024 * 1024;
+    static constexpr int scl = 256;          // float[64] per epilogue warp
+    static constexpr int ostage = scl + kPairEpiWarps * (kPairNT / 4) * 4;   // 1 KB per epilogue warp (output staging)
+    static constexpr int a = (ostage + kPairEpiWarps * kOutStageBytes + 1023) / 1024 * 1024;
     static constexpr int b = a + kPairStages * kPairHalf;
     static constexpr int rest = b + kPairStages * kPairHalf;
     static constexpr int total = 1024 + rest;
@@ -125,7 +127,7 @@ __global__ void __launch_bounds__(PairSmem::threads, 1)
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_acc_full(b), 1);                   // tcgen05.commit after a tile's last MMA
-            mbar_init(bar_acc_empty(b), 2 * kLgEpiWarps);    // the epilogue warps of both CTAs
+            mbar_init(bar_acc_empty(b), 2 * kPairEpiWarps);  // the epilogue warps of both CTAs
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -192,7 +194,7 @@ __global__ void __launch_bounds__(PairSmem::threads, 1)
         // ---------------------------------------------------------- epilogue (both CTAs, own 128 weight rows)
         griddep_wait();  // scales, residual and the output buffer may belong to the previous kernel
         const int quarter = warp & 3;          // the tensor-memory lanes a warp may read: 32 * (warp % 4)
-        constexpr int CW = NT / 2;             // token columns per epilogue warp
+        constexpr int CW = NT / (kPairEpiWarps / 4);   // token columns per epilogue warp
         const int cb = ((warp - kLgFirstEpi) >> 2) * CW;
         float* s_w = s_s + (warp - kLgFirstEpi) * CW;
         const uint32_t ostage = sbase + L::ostage + (uint32_t)((warp - kLgFirstEpi) * kOutStageBytes);
