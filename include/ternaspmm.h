@@ -183,13 +183,14 @@ void bitlinear_TernaSpMM_residual(int8_t* x, uint64_t* bitmap, int* tile_offsets
 
 /* bitlinear_TernaSpMM_residual with the workspace of the reference's prefill path and its size.  The
  * reference's prefill path decompresses the weight into a dense int8 matrix W[N][K] in the workspace
- * before its GEMM (kernels/src/TernaSpMM_API.cuh:262-285), so its callers already hold N*K bytes
- * there (model.py:34-42 allocates the largest layer's).  When workspace_bytes >= N*K and the call has
- * at least 1536 tokens and enough output tiles to fill the chip, this entry decodes the weight once per
- * call into the workspace (which stays in L2 at these sizes) and runs the tcgen05 kernel with both
- * operands by TMA, instead of decoding every weight tile once per 256-token tile on chip; otherwise
- * it behaves like bitlinear_TernaSpMM_residual.  path: 0 = choose, 1 = never use the workspace,
- * 2 = always (needs the N*K bytes).  workspace 128-byte aligned; results are bit-identical either way. */
+ * before its GEMM (kernels/src/TernaSpMM_API.cuh:139-162, 262-285), so its callers already hold N*K
+ * bytes there (model.py:34-42 allocates the largest layer's).  When workspace_bytes >= N*K and the call
+ * has at least 384 tokens (1024 for layers with K > 4096), this entry decodes the weight once per call
+ * into the workspace (which stays in L2 at these sizes) and runs a tcgen05 kernel on CTA pairs
+ * (256 x 256 tiles, both operands by TMA), instead of decoding every weight tile once per 256-token
+ * tile on chip; otherwise it behaves like bitlinear_TernaSpMM_residual.  path: 0 = choose, 1 = never
+ * use the workspace, 2 = always (needs the N*K bytes).  workspace 128-byte aligned; results are
+ * bit-identical either way. */
 void bitlinear_TernaSpMM_ws(int8_t* x, uint64_t* bitmap, int* tile_offsets, uint16_t* quarter_offsets,
                             uint32_t* sign_words, ternaspmm_bf16* out, ternaspmm_bf16* s, ternaspmm_bf16* ws,
                             int ws_num, int M, int N, int K, ternaspmm_bf16* residual, void* workspace,

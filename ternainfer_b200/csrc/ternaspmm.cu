@@ -505,12 +505,17 @@ extern "C" void bitlinear_TernaSpMM_residual(int8_t* x, uint64_t* bitmap, int* t
 // Large-batch path through a dense workspace: decompress once, then the tensor-core kernel with both
 // operands by TMA.  Returns false when the shape is one the on-chip path serves better.
 static bool dense_prefill_pays(int M, int N, int K, long long workspace_bytes) {
-    // Measured on the BitNet-2B layers: decoding once into the workspace wins from about 2048 tokens on
-    // (gate-up at 2048 / 4096 tokens: 87 / 157 us against 94 / 181 us on chip); below that the on-chip
-    // kernel re-decodes little and, for narrow layers, fills the chip with its cluster K split.
-    if (workspace_bytes < (long long)N * K || M < 1536) return false;
-    const long long tiles = (long long)((N + 127) / 128) * ((M + 255) / 256);
-    return tiles * 2 >= device_sm_count();
+    // Measured on the BitNet-2B layers (one call, microseconds, on chip / through the workspace):
+    //   tokens           256          384          512          1024         2048         4096
+    //   3840 x 2560   14.9 / 17.0  18.7 / 17.2  18.9 / 17.7  20.5 / 18.0  32.9 / 24.4  59.0 / 37.8
+    //   13824 x 2560  20.3 / 21.6  31.5 / 27.1  32.0 / 28.0  46.7 / 36.1  87.3 / 58.5  168 / 107
+    //   2560 x 6912   18.0 / 27.5  26.4 / 27.9  26.7 / 28.4  36.4 / 29.0  62.8 / 45.1  91.5 / 61.9
+    // The on-chip kernel decodes every weight tile once per 256 tokens, so from the second token tile on
+    // decoding once into the workspace wins; deep, narrow layers (few output tiles, a long K loop) need
+    // more tokens, because on chip they split K over a cluster and the pair kernel does not.
+    (void)N;
+    if (workspace_bytes < (long long)N * K) return false;
+    return M >= 384 && (K <= 4096 || M >= 1024);
 }
 
 static cudaError_t launch_decompress(const SpmmParams& p, int8_t* dense, cudaStream_t stream) {

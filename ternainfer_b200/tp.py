@@ -138,6 +138,21 @@ def check_status():
         raise RuntimeError(f"TernaSpMM library status {st}" + (" (a wait for a peer rank timed out)" if st == 4 else ""))
 
 
+def announce_leaving(store, rank: int):
+    """Tell the other ranks, through the rendezvous store (host side), that this rank leaves the group.
+    Call it between steps, with none of this rank's kernels or collectives in flight."""
+    store.set(f"tp_rank_left_{rank}", "1")
+
+
+def check_peers(store, rank: int, world: int):
+    """Raise before the next launch if a peer has announced that it left: a step whose collective or
+    fused tail waited for that peer would end in a time-out (status 4) or an error from the
+    process group instead.  Host side only: one store query per peer."""
+    for r in range(world):
+        if r != rank and store.check([f"tp_rank_left_{r}"]):
+            raise RuntimeError(f"tensor-parallel rank {r} has left the group")
+
+
 class _PeerBuffers:
     """One call site's symmetric memory: ``numel`` floats of partials, 16 uint32 flags and
     ``out_numel`` bf16 outputs, mapped into every rank of ``group``, plus two local counters.

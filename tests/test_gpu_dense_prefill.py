@@ -66,7 +66,11 @@ def test_small_and_ragged_shapes_forced_through_the_workspace(lib, M, N, K):
 def test_auto_choice_and_fallbacks(lib):
     kind, _, _ = run_ws(lib, 2048, 13824, 2560, 2, path=0, seed=1)           # big: through the workspace
     assert kind == 7
-    kind, wk, _ = run_ws(lib, 256, 2560, 2560, 1, path=0, seed=2)            # few output tiles: on chip (cluster K split)
+    kind, _, _ = run_ws(lib, 512, 3840, 2560, 3, path=0, seed=5)             # two token tiles already pay
+    assert kind == 7
+    kind, wk, _ = run_ws(lib, 256, 2560, 2560, 1, path=0, seed=2)            # one token tile: on chip (cluster K split)
+    assert kind == 3 and (wk == 0x55).all()
+    kind, wk, _ = run_ws(lib, 512, 2560, 6912, 1, path=0, seed=6)            # deep and narrow: on chip up to 1024 tokens
     assert kind == 3 and (wk == 0x55).all()
     kind, wk, _ = run_ws(lib, 64, 13824, 2560, 2, path=0, seed=3)            # decode-sized: never
     assert kind in (1, 2, 3) and (wk == 0x55).all()
