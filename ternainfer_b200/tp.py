@@ -340,3 +340,27 @@ def shard_checkpoint_entry(dic: dict, key: str, w_int8: torch.Tensor, ws: torch.
     dic[key + ".weight_TileOffsets_median"], dic[key + ".weight_bitmap"] = tm, bm
     dic[key + ".weight_scale"] = ws
     return local
+
+
+def shard_model_checkpoint(dic: dict, n_layers: int, rank: int, tp: int) -> dict:
+    """This rank's checkpoint of a whole model from an unsharded one that still holds the ternary
+    weights (``<key>.weight_int8``, as ``random_checkpoint(dense=True)`` returns them): QKV and gate-up
+    column-parallel by scale segment (whole heads per rank), O and down row-parallel with the matching
+    slice of the sub-layer norm weight; norms, embedding and scales are replicated."""
+    out = {k: v for k, v in dic.items() if not k.startswith("layers.")}
+    kinds = (("attention.wqkv", "column"), ("attention.wo", "row"), ("feed_forward.w13", "column"),
+             ("feed_forward.w2", "row"))
+    for i in range(n_layers):
+        p = f"layers.{i}."
+        for name, kind in kinds:
+            key = p + name
+            w = dic[key + ".weight_int8"]
+            segs = dic.get(key + ".weight_segments")
+            segs = [int(v) for v in segs.tolist()] if segs is not None else [w.shape[0]]
+            shard_checkpoint_entry(out, key, w, dic[key + ".weight_scale"], segs, kind, rank, tp)
+        out[p + "attention.attn_sub_norm.weight"] = shard_vector(dic[p + "attention.attn_sub_norm.weight"], rank, tp)
+        out[p + "feed_forward.ffn_sub_norm.weight"] = shard_vector(dic[p + "feed_forward.ffn_sub_norm.weight"], rank, tp)
+        out[p + "attention_norm.weight"] = dic[p + "attention_norm.weight"]
+        out[p + "ffn_norm.weight"] = dic[p + "ffn_norm.weight"]
+    return out
+
