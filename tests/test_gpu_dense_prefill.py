@@ -15,7 +15,7 @@ from gpu_util import Packed, dev
 pytestmark = pytest.mark.gpu
 
 
-def run_ws(lib, M, N, K, ws_num, path, seed, residual=False, slack=0):
+def run_ws(lib, M, N, K, ws_num, path, seed, residual=False, slack=0, skew=0):
     w = o.make_ternary(N, K, 0.45, seed)
     xq, s = o.make_activations(M, K, seed + 1)
     ws = o.make_ws(ws_num, seed + 2)
@@ -28,15 +28,17 @@ def run_ws(lib, M, N, K, ws_num, path, seed, residual=False, slack=0):
         res_d = dev(o.f32_to_bf16_bits(res))
         want = o.f32_to_bf16_bits(res + o.bf16_bits_to_f32(want))
     x_d, s_d, ws_d = dev(xq), dev(sb), dev(wb)
-    out = torch.full((M * N + 128,), 0x7B7B, dtype=torch.int16, device="cuda")
+    out = torch.full((M * N + 128 + skew,), 0x7B7B, dtype=torch.int16, device="cuda")
     work = torch.full((N * K + slack + 256,), 0x55, dtype=torch.int8, device="cuda")
     lib.bitlinear_TernaSpMM_ws(x_d.data_ptr(), pk.bm.data_ptr(), pk.tg.data_ptr(), pk.tm.data_ptr(), pk.cv.data_ptr(),
-                               out.data_ptr(), s_d.data_ptr(), ws_d.data_ptr(), ws_num, M, N, K,
+                               out.data_ptr() + 2 * skew, s_d.data_ptr(), ws_d.data_ptr(), ws_num, M, N, K,
                                res_d.data_ptr() if res_d is not None else None, work.data_ptr(), N * K + slack, path,
                                torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
     assert lib.ternaspmm_last_status() == 0
     got = out.cpu().numpy().view(np.uint16)
+    assert (got[:skew] == 0x7B7B).all(), "wrote in front of the output"
+    got = got[skew:]
     assert (got[M * N:] == 0x7B7B).all(), "wrote past the output"
     assert (got[:M * N].reshape(M, N) == want).all(), "bf16 outputs differ from the oracle"
     shape = (ctypes.c_int * 6)()
@@ -61,6 +63,14 @@ def test_small_and_ragged_shapes_forced_through_the_workspace(lib, M, N, K):
     kind, wk, w = run_ws(lib, M, N, K, 2, path=2, seed=M + N + K, residual=True)
     assert kind == (7 if M > 128 else 6)
     assert (wk[:N * K].reshape(N, K) == w).all()
+
+
+@pytest.mark.parametrize("M,path", [(300, 2), (100, 2), (300, 1), (100, 1)])
+def test_output_that_is_not_16_byte_aligned(lib, M, path):
+    """The bf16 epilogues store 16 bytes per lane when the output (and residual) allow it; an output that
+    starts at an odd element takes the two-byte stores instead.  Same bits, nothing written outside."""
+    run_ws(lib, M, 320, 256, 2, path=path, seed=M + path, skew=3)
+    run_ws(lib, M, 320, 256, 2, path=path, seed=M + path + 1, skew=8, residual=True)
 
 
 def test_auto_choice_and_fallbacks(lib):
