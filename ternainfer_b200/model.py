@@ -264,14 +264,15 @@ class Transformer(nn.Module):
             self._rope = rope_tables(self.args.head_dim, self.max_seq_len, self.args.rope_theta, tokens.device)
             self._rope_lp = (self._rope[0].to(torch.bfloat16), self._rope[1].to(torch.bfloat16))
         B, T = tokens.shape
-        cos, sin = self._rope[0][pos].expand(B, T, -1), self._rope[1][pos].expand(B, T, -1)
-        keys = torch.arange(self.max_seq_len, device=tokens.device)
-        mask = (keys[None, :] <= pos[:, None])[None, None]          # [1, 1, T, L] causal over cache positions
         h = self.tok_embeddings(tokens)
         fused = self.args.fused_glue and self.tp == 1
-        flash = None
-        if self.flash:
+        flash, cos, sin, mask = None, None, None, None
+        if self.flash:   # the kv-cache kernel applies RoPE from the tables and masks by sequence length itself
             flash = (pos[:1].to(torch.int32).expand(B).contiguous(), self._rope_lp[0], self._rope_lp[1])
+        else:
+            cos, sin = self._rope[0][pos].expand(B, T, -1), self._rope[1][pos].expand(B, T, -1)
+            keys = torch.arange(self.max_seq_len, device=tokens.device)
+            mask = (keys[None, :] <= pos[:, None])[None, None]      # [1, 1, T, L] causal over cache positions
         for layer, c in zip(self.layers, cache):
             h = layer(h, c, pos, cos, sin, mask, fused, flash)
         if greedy_last:
