@@ -210,6 +210,14 @@ void ternaspmm_rmsnorm_quant(ternaspmm_bf16* x, ternaspmm_bf16* norm_weight, flo
 void ternaspmm_relu2_gate_rmsnorm_quant(ternaspmm_bf16* x13, ternaspmm_bf16* norm_weight, float eps, int M,
                                         int K, int8_t* q, ternaspmm_bf16* s_out, ternaspmm_stream_t stream);
 
+/* RMSNorm alone, in the summation order of ternaspmm_rmsnorm_quant: y = bf16((x * rstd) * norm_weight),
+ * rstd = 1 / sqrt(sum(x^2) / K + eps).  One launch instead of the chain of elementwise kernels of an
+ * eager RMSNorm (the model's final norm in front of the output head, model.py:385 of the reference).
+ * x, y bf16 [M][K] (y may alias x), norm_weight bf16 [K]; K a multiple of 16, at most 57344; 16-byte
+ * aligned pointers. */
+void ternaspmm_rmsnorm(ternaspmm_bf16* x, ternaspmm_bf16* norm_weight, float eps, int M, int K, ternaspmm_bf16* y,
+                       ternaspmm_stream_t stream);
+
 /* Plain per-token absmax quantiser (model.py:120-123) as one kernel. */
 void ternaspmm_quant(ternaspmm_bf16* x, int M, int K, int8_t* q, ternaspmm_bf16* s_out,
                      ternaspmm_stream_t stream);

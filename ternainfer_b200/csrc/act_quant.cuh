@@ -47,7 +47,9 @@ __device__ __forceinline__ float block_reduce(float v, float* scratch, bool is_m
 // MODE 0: y = RMSNorm(v) * w.  MODE 1: y = v * w without the normalisation, and the row's sum
 // of squares of v is written to ss_out (tensor-parallel row shards: the RMS factor needs the sum
 // over all shards and is applied after the all-reduce).  MODE 2: y = v (plain quantiser).
-enum ActMode : int { ACT_RMSNORM = 0, ACT_SCALE_SUMSQ = 1, ACT_PLAIN = 2 };
+// MODE 3: y = RMSNorm(v) * w written out as bf16 to `q` (read as bf16 [M][K]), no quantiser: the
+// model's final norm in the same fixed summation order.
+enum ActMode : int { ACT_RMSNORM = 0, ACT_SCALE_SUMSQ = 1, ACT_PLAIN = 2, ACT_NORM_ONLY = 3 };
 
 // x: [M][ld] bf16 (GATED: the row holds [x1 (K) | x3 (K)], ld = 2K), w: [K] bf16 norm weight,
 // q: [M][K] int8, s_out: [M] bf16, ss_out: [M] fp32 (MODE 1).  Dynamic shared memory: K bf16.
@@ -94,7 +96,7 @@ __global__ void __launch_bounds__(kActMaxThreads) norm_quant_kernel(const __nv_b
     float rstd = 1.f;
     if (MODE != ACT_PLAIN) {
         ss = block_reduce(ss, scratch, false);
-        if (MODE == ACT_RMSNORM) rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)K), eps)));
+        if (MODE == ACT_RMSNORM || MODE == ACT_NORM_ONLY) rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)K), eps)));
         if (MODE == ACT_SCALE_SUMSQ && tid == 0) ss_out[t] = ss;
     }
 
@@ -108,15 +110,17 @@ __global__ void __launch_bounds__(kActMaxThreads) norm_quant_kernel(const __nv_b
             const __nv_bfloat16* ww = reinterpret_cast<const __nv_bfloat16*>(&wv);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const float y = __fmul_rn(MODE == ACT_RMSNORM ? __fmul_rn(__bfloat162float(av[i]), rstd) : __bfloat162float(av[i]),
+                const float y = __fmul_rn((MODE == ACT_RMSNORM || MODE == ACT_NORM_ONLY) ? __fmul_rn(__bfloat162float(av[i]), rstd) : __bfloat162float(av[i]),
                                           __bfloat162float(ww[i]));
                 av[i] = __float2bfloat16_rn(y);
             }
-            *reinterpret_cast<uint4*>(row + k0) = a;
+            if (MODE == ACT_NORM_ONLY) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(q) + (size_t)t * K + k0) = a;
+            else *reinterpret_cast<uint4*>(row + k0) = a;
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(__bfloat162float(av[i])));
     }
+    if (MODE == ACT_NORM_ONLY) return;
     amax = block_reduce(amax, scratch, true);
     amax = bf16_round_f(fmaxf(amax, 1e-5f));
     const float s = bf16_round_f(bf16_round_f(1.0f / amax) * 127.0f);   // 127 / amax as reciprocal * 127, in bf16

@@ -637,7 +637,7 @@ static void run_norm_quant(bool gated, int mode, __nv_bfloat16* x, __nv_bfloat16
         t_host_status = ST_BAD_SHAPE;
         return;
     }
-    if (!x || (mode != ACT_PLAIN && !w) || !q || !s_out || (mode == ACT_SCALE_SUMSQ && !ss_out) ||
+    if (!x || (mode != ACT_PLAIN && !w) || !q || (!s_out && mode != ACT_NORM_ONLY) || (mode == ACT_SCALE_SUMSQ && !ss_out) ||
         (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
         (reinterpret_cast<uintptr_t>(q) & 15)) {
         fprintf(stderr, "ternaspmm: norm_quant: null or misaligned pointer\n");
@@ -646,6 +646,7 @@ static void run_norm_quant(bool gated, int mode, __nv_bfloat16* x, __nv_bfloat16
     }
     typedef void (*Kern)(const __nv_bfloat16*, const __nv_bfloat16*, float, int, int8_t*, __nv_bfloat16*, float*);
     Kern kern = gated ? (mode == ACT_RMSNORM ? norm_quant_kernel<true, ACT_RMSNORM> : norm_quant_kernel<true, ACT_SCALE_SUMSQ>)
+                      : mode == ACT_NORM_ONLY ? norm_quant_kernel<false, ACT_NORM_ONLY>
                       : (mode == ACT_RMSNORM ? norm_quant_kernel<false, ACT_RMSNORM>
                                              : (mode == ACT_SCALE_SUMSQ ? norm_quant_kernel<false, ACT_SCALE_SUMSQ>
                                                                         : norm_quant_kernel<false, ACT_PLAIN>));
@@ -682,6 +683,12 @@ extern "C" void ternaspmm_rmsnorm_quant(__nv_bfloat16* x, __nv_bfloat16* norm_we
 extern "C" void ternaspmm_relu2_gate_rmsnorm_quant(__nv_bfloat16* x13, __nv_bfloat16* norm_weight, float eps, int M,
                                                   int K, int8_t* q, __nv_bfloat16* s_out, cudaStream_t stream) {
     run_norm_quant(true, ACT_RMSNORM, x13, norm_weight, eps, M, K, q, s_out, nullptr, stream);
+    checkLastCudaError(__LINE__);
+}
+
+extern "C" void ternaspmm_rmsnorm(__nv_bfloat16* x, __nv_bfloat16* norm_weight, float eps, int M, int K, __nv_bfloat16* y,
+                                  cudaStream_t stream) {
+    run_norm_quant(false, ACT_NORM_ONLY, x, norm_weight, eps, M, K, reinterpret_cast<int8_t*>(y), nullptr, nullptr, stream);
     checkLastCudaError(__LINE__);
 }
 

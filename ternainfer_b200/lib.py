@@ -93,6 +93,8 @@ def load_library() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = [_P, _P, ctypes.c_float, _I, _I, _P, _P, _P]
         fn.restype = None
+    lib.ternaspmm_rmsnorm.argtypes = [_P, _P, ctypes.c_float, _I, _I, _P, _P]
+    lib.ternaspmm_rmsnorm.restype = None
     lib.ternaspmm_quant.argtypes = [_P, _I, _I, _P, _P, _P]
     lib.ternaspmm_quant.restype = None
     lib.ternaspmm_scale_quant_sumsq.argtypes = [_P, _P, _I, _I, _I, _P, _P, _P, _P]
@@ -125,6 +127,6 @@ EXPORTED_SYMBOLS = (
     "ternaspmm_lm_head_argmax_noalloc",
     "ternaspmm_list_plan", "ternaspmm_list_create", "ternaspmm_list_run", "ternaspmm_list_destroy",
     "ternaspmm_accumulate_i32", "ternaspmm_linear_segments", "bitlinear_TernaSpMM_residual", "bitlinear_TernaSpMM_ws", "ternaspmm_quant",
-    "ternaspmm_scale_quant_sumsq", "ternaspmm_partial_f32", "ternaspmm_tp_finish", "ternaspmm_tp_allreduce_finish", "ternaspmm_rmsnorm_quant", "ternaspmm_relu2_gate_rmsnorm_quant", "ternaspmm_pack_i8",
+    "ternaspmm_scale_quant_sumsq", "ternaspmm_partial_f32", "ternaspmm_tp_finish", "ternaspmm_tp_allreduce_finish", "ternaspmm_rmsnorm_quant", "ternaspmm_relu2_gate_rmsnorm_quant", "ternaspmm_rmsnorm", "ternaspmm_pack_i8",
     "ternaspmm_unpack_i8", "ternaspmm_transcode_reference_layout",
 )

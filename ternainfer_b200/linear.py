@@ -86,6 +86,19 @@ def rmsnorm_quant(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, gated:
     return q.reshape(*x.shape[:-1], K), s.reshape(*x.shape[:-1], 1)
 
 
+def rmsnorm(x: torch.Tensor, norm_weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm(x) * weight in one kernel, in the summation order of ``rmsnorm_quant``; bf16 in, bf16 out."""
+    if not x.is_cuda:
+        raise RuntimeError("rmsnorm needs CUDA tensors: the B200 library has no CPU path")
+    lib = load_library()
+    K = norm_weight.shape[0]
+    x2 = x.reshape(-1, K).contiguous()
+    y = torch.empty_like(x2)
+    lib.ternaspmm_rmsnorm(x2.data_ptr(), norm_weight.data_ptr(), float(eps), x2.shape[0], K, y.data_ptr(),
+                          torch.cuda.current_stream().cuda_stream)
+    return y.reshape(x.shape)
+
+
 _HEAD_SCRATCH = {}
 
 

@@ -20,7 +20,7 @@ import torch
 from torch import nn
 from torch.nn import functional as F
 
-from .linear import SpBitLinear, quant_input, rmsnorm_quant, lm_head_argmax
+from .linear import SpBitLinear, quant_input, rmsnorm, rmsnorm_quant, lm_head_argmax
 
 
 @dataclass
@@ -247,7 +247,10 @@ class Transformer(nn.Module):
         Up to 8 rows run on the library's head kernel (one pass over the embedding, arg-max fused);
         more rows use the dense bf16 GEMM."""
         B, T = h.shape[0], h.shape[1]
-        h = self.norm(h)
+        if self.args.fused_glue and h.is_cuda and h.dtype == torch.bfloat16 and h.shape[-1] % 16 == 0:
+            h = rmsnorm(h, self.norm.weight, self.norm.eps)   # one launch, the fused front-ends' summation order
+        else:
+            h = self.norm(h)
         emb = self.tok_embeddings.weight
         if h.is_cuda and B * T <= 8 and emb.dtype == torch.bfloat16 and h.dtype == torch.bfloat16 and h.shape[-1] % 32 == 0:
             logits, toks = lm_head_argmax(h, emb, want_logits=not greedy, want_argmax=greedy)

@@ -97,7 +97,7 @@ def ordered_norm_quant(x, w, eps, gated=False):
 
 def build_pair_same_glue(n_layers, vocab, seed=7, max_len=96):
     """(fused-glue model on this library's kernels, the SAME model in eager torch with every ternary
-    linear on the exact reference formula and every in-layer norm in the fused kernels' stated
+    linear on the exact reference formula and every norm in the fused kernels' stated
     order).  Both use flash_attn's kv-cache kernel for the attention glue (library code)."""
     import types
     from ternainfer_b200.model import ModelArgs, Transformer, RMSNorm
@@ -113,10 +113,9 @@ def build_pair_same_glue(n_layers, vocab, seed=7, max_len=96):
     def fwd(self, x):
         return ordered_norm(x, self.weight, self.eps)
 
-    for layer in ref.layers:
-        for m in layer.modules():
-            if isinstance(m, RMSNorm):
-                m.forward = types.MethodType(fwd, m)
+    for m in ref.modules():      # every norm of the model, the final one in front of the output head included
+        if isinstance(m, RMSNorm):
+            m.forward = types.MethodType(fwd, m)
     return fused, ref
 
 
@@ -158,6 +157,22 @@ def torch_norm_quant(x, w, eps, gated=False):
     xf = x.float()
     y = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(x.dtype)
     return quant_input(y)
+
+
+@pytest.mark.parametrize("M,K", [(1, 2560), (8, 2560), (300, 2560), (5, 28672), (3, 64), (2, 8192)])
+def test_rmsnorm_kernel_bit_exact_against_its_stated_order(lib, M, K):
+    """ternaspmm_rmsnorm (the model's final norm in fused-glue mode): every bf16 output equals the
+    restatement of its summation order; in place too."""
+    from ternainfer_b200.linear import rmsnorm
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + K)
+    x = (torch.randn((M, K), generator=g, device="cuda") * 3).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(K, generator=g, device="cuda")).to(torch.bfloat16)
+    want = ordered_norm(x, w, 1e-5)
+    assert torch.equal(rmsnorm(x, w, 1e-5), want)
+    y = x.clone()
+    lib.ternaspmm_rmsnorm(y.data_ptr(), w.data_ptr(), 1e-5, M, K, y.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert lib.ternaspmm_last_status() == 0 and torch.equal(y, want)
 
 
 @pytest.mark.parametrize("gated", [False, True])
