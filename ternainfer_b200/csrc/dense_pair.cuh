@@ -152,7 +152,7 @@ __global__ void __launch_bounds__(PairSmem::threads, 1)
                 const int t0 = (tile / RB) * NT + (int)crank * 128;          // this CTA's tokens
                 for (int ks = 0; ks < KS; ++ks, ++gs) {
                     const int s = gs % ST, it = gs / ST;
-                    if (it > 0) ok = wait_or_abort_hot(bar_empty(s), (it - 1) & 1, abort_flag);
+                    if (it > 0) ok = wait_or_abort(bar_empty(s), (it - 1) & 1, abort_flag);
                     if (!ok) break;
                     const uint32_t full = map_to_rank(bar_full(s), 0);
                     if (crank == 0) mbar_arrive_expect_tx(bar_full(s), (PAIR_ABLATE(2) ? 0 : 2 * kPairHalf) + (PAIR_ABLATE(4) ? 0 : 2 * kPairHalf));
@@ -170,14 +170,14 @@ __global__ void __launch_bounds__(PairSmem::threads, 1)
             for (int ti = 0; ti < my_tiles && ok; ++ti) {
                 const int buf = ti & 1, use = ti >> 1;
                 if (use > 0) {   // both CTAs' epilogues must have drained this accumulator buffer
-                    ok = wait_or_abort_hot(bar_acc_empty(buf), (use - 1) & 1, abort_flag);
+                    ok = wait_or_abort(bar_acc_empty(buf), (use - 1) & 1, abort_flag);
                     if (!ok) break;
                     tc_fence_after();
                 }
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * NT);
                 for (int ks = 0; ks < KS; ++ks, ++gs) {
                     const int s = gs % ST, it = gs / ST;
-                    ok = wait_or_abort_hot(bar_full(s), it & 1, abort_flag);
+                    ok = wait_or_abort(bar_full(s), it & 1, abort_flag);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t a_addr = sbase + L::a + s * kPairHalf, b_addr = sbase + L::b + s * kPairHalf;

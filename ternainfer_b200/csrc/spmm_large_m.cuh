@@ -123,24 +123,25 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 
+// Bounded wait for a phase of an mbarrier.  mbarrier.try_wait suspends the thread in hardware for a short,
+// system-dependent time and wakes it when the phase completes, so a poll is cheap; after a first burst the
+// thread also looks at the CTA's abort flag and sleeps briefly between polls.  The limit is TIME on the
+// global timer (the duration of a poll is not specified, so an iteration count alone bounds nothing): when
+// it runs out the CTA-wide abort flag is raised, every role leaves its loop and the kernel ends with status 4.
+constexpr unsigned long long kLgWaitLimitNs = 2000ull * 1000ull * 1000ull;
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t it = 0; it < (1u << 22); ++it) {
+    unsigned long long t0 = 0;
+    for (uint32_t it = 0; it < (1u << 28); ++it) {
         if (mbar_test(bar, parity)) return true;
-        if (it > 32) {
+        if (it >= 32) {
             if (*abort_flag) return false;
+            if ((it & 63u) == 32u) {
+                const unsigned long long now = global_timer_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > kLgWaitLimitNs) break;
+            }
             __nanosleep(64);
         }
-    }
-    *abort_flag = 1;
-    return false;
-}
-// The same for the single threads on the critical path (operand loader, MMA issuer): no sleep between
-// the polls - mbarrier.try_wait suspends the thread in hardware and wakes it when the phase completes,
-// whereas a sleeping thread notices the completion only when its timer runs out.
-__device__ __forceinline__ bool wait_or_abort_hot(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t it = 0; it < (1u << 24); ++it) {
-        if (mbar_test(bar, parity)) return true;
-        if ((it & 255u) == 255u && *abort_flag) return false;
     }
     *abort_flag = 1;
     return false;
