@@ -171,3 +171,45 @@ def test_shard_helpers():
     assert torch.equal(b, w[:, 64:])
     with pytest.raises(AssertionError):
         tp.shard_rows(w, [7, 3, 2], 0, 2)
+
+
+def test_sharded_model_checkpoint_reassembles_the_unsharded_weights():
+    """shard_model_checkpoint (CPU): the ranks' packed shards, decoded again and put back together, are the
+    unsharded ternary weights - QKV and gate-up split by rows of every scale segment (whole heads per rank),
+    O and down by columns - and the sub-layer norm weights are sliced like the columns they scale."""
+    from ternainfer_b200 import tp
+    from ternainfer_b200.convert import decompress_weight
+    from ternainfer_b200.convert.convert_TernaInfer import random_checkpoint
+    dim, H, Hkv, ffn, world = 256, 4, 2, 512, 2
+    D = dim // H
+    full = random_checkpoint(dim, 1, H, Hkv, ffn, 64, seed=3, device="cpu", dense=True)
+    shards = [tp.shard_model_checkpoint(full, 1, r, world) for r in range(world)]
+
+    def dense(dic, key, n, k):
+        assert dic[key + ".weight_bitmap"].numel() * 64 == n * k
+        return decompress_weight(dic[key + ".weight_compressed_val"], dic[key + ".weight_TileOffsets_global"],
+                                 dic[key + ".weight_TileOffsets_median"], dic[key + ".weight_bitmap"], n, k)
+
+    p = "layers.0."
+    wqkv = full[p + "attention.wqkv.weight_int8"]
+    q, k, v = wqkv[:H * D], wqkv[H * D:(H + Hkv) * D], wqkv[(H + Hkv) * D:]
+    for r in range(world):
+        got = torch.as_tensor(dense(shards[r], p + "attention.wqkv", (H + 2 * Hkv) * D // world, dim))
+        want = torch.cat([q[r * H * D // world:(r + 1) * H * D // world], k[r * Hkv * D // world:(r + 1) * Hkv * D // world],
+                          v[r * Hkv * D // world:(r + 1) * Hkv * D // world]])
+        assert torch.equal(got, want)
+        assert shards[r][p + "attention.wqkv.weight_segments"].tolist() == [H * D // world, Hkv * D // world, Hkv * D // world]
+    for name, kind in (("attention.wo", "row"), ("feed_forward.w2", "row"), ("feed_forward.w13", "column")):
+        w = full[p + name + ".weight_int8"]
+        n, k = (w.shape[0], w.shape[1] // world) if kind == "row" else (w.shape[0] // world, w.shape[1])
+        parts = [torch.as_tensor(dense(shards[r], p + name, n, k)) for r in range(world)]
+        if kind == "row":
+            assert torch.equal(torch.cat(parts, dim=1), w)
+        else:   # [gate | up]: each rank holds its rows of both halves
+            half = w.shape[0] // 2
+            for r in range(world):
+                lo, hi = r * half // world, (r + 1) * half // world
+                assert torch.equal(parts[r], torch.cat([w[lo:hi], w[half + lo:half + hi]]))
+    for key in ("attention.attn_sub_norm.weight", "feed_forward.ffn_sub_norm.weight"):
+        assert torch.equal(torch.cat([shards[r][p + key] for r in range(world)]), full[p + key])
+    assert torch.equal(shards[1]["tok_embeddings.weight"], full["tok_embeddings.weight"])
