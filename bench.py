@@ -591,9 +591,11 @@ def prefill_leg(env, args, token_counts=(256, 1024, 2048, 4096)):
         peak_tf = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
     except Exception:
         pass
-    out = {"layer": "gate-up 13824x2560", "note": "int8 tensor-core ops 2*M*N*K per call; fractions are of the measured "
-           "bf16 cuBLAS burst peak (the int8 rate of the part is twice the bf16 one: 4.1 P op/s in a tcgen05 issue-rate "
-           "probe with resident operands)"}
+    rate = float(lib.ternaspmm_debug_int8_mma_rate(6400, torch.cuda.current_stream().cuda_stream)) / 1e12
+    out = {"layer": "gate-up 13824x2560", "note": "int8 tensor-core ops 2*M*N*K per call; frac_of_measured_bf16_peak is of "
+           "the measured bf16 cuBLAS burst peak, frac_of_int8_issue_rate of the rate at which this GPU issues tcgen05 int8 "
+           "MMAs from resident operands (measured here, one CTA per SM)",
+           "int8_mma_issue_rate_TOPs": rate}
     for M in token_counts:
         xq = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=env.device)
         sc = (torch.rand(M, device=env.device) * 50 + 1).to(torch.bfloat16)
@@ -619,6 +621,7 @@ def prefill_leg(env, args, token_counts=(256, 1024, 2048, 4096)):
         out[str(M)] = {"on_chip_us": t_chip, "workspace_us": t_ws, "auto": "workspace" if shape[0] in (6, 7) else "on_chip",
                        "torch_bf16_linear_us": t_torch,
                        "tensor_TOPs": ops / best / 1e6, "frac_of_measured_bf16_peak": (ops / best / 1e6 / peak_tf) if peak_tf else None,
+                       "frac_of_int8_issue_rate": (ops / best / 1e6 / rate) if rate > 0 else None,
                        "speedup_vs_torch_bf16": t_torch / best}
     del w, wd, work
     torch.cuda.empty_cache()

@@ -142,6 +142,12 @@ int ternaspmm_last_status(void);
  * (default 1000, clamped to 1..10000).  Process-wide. */
 void ternaspmm_set_wait_limit_ms(int ms);
 
+/* Measurement hook: int8 tensor-core operations per second that the GPU issues with tcgen05.mma
+ * (128 x 256 x 32 per instruction, operands resident in shared memory, one CTA per SM, `iters` groups of
+ * four instructions per SM) - the ceiling that the tensor-core kernels of this library are quoted
+ * against in bench.py.  Synchronises the stream; returns 0 on failure. */
+double ternaspmm_debug_int8_mma_rate(int iters, ternaspmm_stream_t stream);
+
 /* Test hook: shape of the most recent kernel launch made by this thread.
  * out6 = {kernel (1 = small-batch kernel, one fat CTA per SM; 2 = small-batch
  * kernel, thin CTAs; 3 = tcgen05 kernel; 4 = output head; 5 = work list; 6 = tcgen05 kernel

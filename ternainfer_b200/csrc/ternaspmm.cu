@@ -20,6 +20,7 @@
 #include "dense_pair.cuh"
 #include "dense_prefill.cuh"
 #include "lm_head.cuh"
+#include "mma_rate_probe.cuh"
 #include "spmm_large_m.cuh"
 #include "spmm_list.cuh"
 #include "spmm_small_m.cuh"
@@ -1076,6 +1077,35 @@ extern "C" void ternaspmm_lm_head_argmax_noalloc(__nv_bfloat16* h, __nv_bfloat16
 
 extern "C" void ternaspmm_debug_inject_host_failure(int kind) {
     if (kind == 1) t_inject_encode_failure = 1;
+}
+
+extern "C" int ternaspmm_last_status(void);
+
+// Measurement hook (see mma_rate_probe.cuh): int8 tensor-core operations per second that this GPU issues
+// from shared-memory operands, over all SMs; 0 on failure.  Synchronises the stream.
+extern "C" double ternaspmm_debug_int8_mma_rate(int iters, cudaStream_t stream) {
+    t_host_status = ST_OK;
+    if (iters < 64) iters = 64;
+    iters = (iters + 63) / 64 * 64;
+    int* status = status_device_ptr();
+    const int smem_bytes = 1024 + 1024 + kLgAStage + 256 * kLgKStep;
+    if (!status || cudaFuncSetAttribute(int8_mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) {
+        t_host_status = ST_LAUNCH;
+        return 0.0;
+    }
+    const int sms = device_sm_count();
+    cudaEvent_t e0, e1;
+    if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return 0.0;
+    int8_mma_rate_kernel<<<sms, 128, smem_bytes, stream>>>(64, status);   // warm-up
+    cudaEventRecord(e0, stream);
+    int8_mma_rate_kernel<<<sms, 128, smem_bytes, stream>>>(iters, status);
+    cudaEventRecord(e1, stream);
+    float ms = 0.f;
+    const bool ok = cudaEventSynchronize(e1) == cudaSuccess && cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess && ms > 0.f;
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (!ok || ternaspmm_last_status() != 0) return 0.0;
+    return 2.0 * 128 * 256 * 32 * 4.0 * iters * sms / (ms * 1e-3);
 }
 
 extern "C" void ternaspmm_set_wait_limit_ms(int ms) {

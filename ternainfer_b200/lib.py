@@ -94,6 +94,8 @@ def load_library() -> ctypes.CDLL:
         fn.argtypes = [_P, _P, ctypes.c_float, _I, _I, _P, _P, _P]
         fn.restype = None
     lib.ternaspmm_rmsnorm.argtypes = [_P, _P, ctypes.c_float, _I, _I, _P, _P]
+    lib.ternaspmm_debug_int8_mma_rate.argtypes = [_I, _P]
+    lib.ternaspmm_debug_int8_mma_rate.restype = ctypes.c_double
     lib.ternaspmm_rmsnorm.restype = None
     lib.ternaspmm_quant.argtypes = [_P, _I, _I, _P, _P, _P]
     lib.ternaspmm_quant.restype = None
@@ -123,7 +125,7 @@ EXPORTED_SYMBOLS = (
     "bitlinear_TernaSpMM", "bitlinear_TernaSpMM_decode", "bitlinear_TernaSpMM_prefill",
     "bitlinear_TernaSpMM_benchmark", "checkLastCudaError", "reorder_WT_h", "convert_reorderd",
     "gpu_sleep", "ternaspmm_last_status", "ternaspmm_set_wait_limit_ms", "ternaspmm_last_launch_shape",
-    "ternaspmm_debug_inject_host_failure", "ternaspmm_lm_head_argmax", "ternaspmm_lm_head_scratch_bytes",
+    "ternaspmm_debug_inject_host_failure", "ternaspmm_debug_int8_mma_rate", "ternaspmm_lm_head_argmax", "ternaspmm_lm_head_scratch_bytes",
     "ternaspmm_lm_head_argmax_noalloc",
     "ternaspmm_list_plan", "ternaspmm_list_create", "ternaspmm_list_run", "ternaspmm_list_destroy",
     "ternaspmm_accumulate_i32", "ternaspmm_linear_segments", "bitlinear_TernaSpMM_residual", "bitlinear_TernaSpMM_ws", "ternaspmm_quant",

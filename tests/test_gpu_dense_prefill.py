@@ -127,3 +127,11 @@ def test_python_call_site_uses_the_workspace_at_prefill(lib):
     _, want = c_oracle.ternaspmm(xq, w, o.f32_to_bf16_bits(s.reshape(-1)), o.f32_to_bf16_bits(wsv), 2, -1)
     assert (y.view(torch.int16).cpu().numpy().view(np.uint16) == want).all()
     assert get_global_workspace("cuda").numel() >= N * K
+
+
+def test_int8_mma_issue_rate_hook(lib):
+    """The measurement hook that bench.py quotes the tensor-core kernels against: returns a plausible rate
+    (the part issues int8 MMAs at about twice its bf16 rate) and leaves the status word clean."""
+    rate = lib.ternaspmm_debug_int8_mma_rate(3200, torch.cuda.current_stream().cuda_stream)
+    assert lib.ternaspmm_last_status() == 0
+    assert 1.0e15 < rate < 8.0e15, rate
