@@ -549,7 +549,8 @@ extern "C" void bitlinear_TernaSpMM_ws(int8_t* x, uint64_t* bitmap, int* tile_of
                                        int ws_num, int M, int N, int K, __nv_bfloat16* residual, void* workspace,
                                        long long workspace_bytes, int path, cudaStream_t stream) {
     const int epilogue = M <= 64 ? EPI_DECODE : EPI_PREFILL;
-    const bool dense = path == 2 || (path == 0 && workspace && dense_prefill_pays(M, N, K, workspace_bytes));
+    const bool dense = path == 2 || (path == 0 && workspace && !(reinterpret_cast<uintptr_t>(workspace) & 127) &&
+                                    dense_prefill_pays(M, N, K, workspace_bytes));   // (a workspace that cannot be used is not an error)
     if (!dense) {
         run_spmm(x, bitmap, tile_offsets, quarter_offsets, sign_words, out, s, ws, ws_num, M, N, K, epilogue, stream, nullptr,
                  residual);
