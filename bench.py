@@ -15,11 +15,14 @@ activations + scales + bf16 outputs) of all ranks per second with every input
 resident in HBM, the step replayed as a CUDA graph; ``e2e`` = the same metric
 through the Python call site (``TernaInfer_linear``) with the activations
 copied from pinned host memory and the outputs copied back every step.
-On one GPU the line also carries ``by_tokens`` (the same sweep at 1 and 16
-tokens), ``ref_kernels_b200`` (the reference's own small-batch CUDA kernels,
-built for sm_100a from the reference checkout, timed in the same loop at 8, 16
-and 64 tokens next to this library) and ``decode`` (greedy decode tokens/s of
-the 30-layer model at batch 1 and 8).  On N > 1 GPUs the sweep runs as
+On one GPU the line also carries ``list_entry`` (the same step as ONE persistent
+launch over a work list), ``by_tokens`` (the same sweep at 1 and 16 tokens),
+``ref_kernels_b200`` (the reference's own small-batch CUDA kernels, built for
+sm_100a from the reference checkout, timed in the same loop at 8, 16 and 64
+tokens next to this library), ``lm_head`` (output head + greedy token),
+``prefill`` (the large-batch paths against a bf16 GEMM and against the measured
+int8 tensor-core issue rate) and ``decode`` (greedy decode tokens/s of the
+30-layer model at batch 1 and 8).  On N > 1 GPUs the sweep runs as
 independent replicas (the 2B model's 5 KV heads do not shard) and the line
 carries ``tp``: the sharded linear stack of the 8192-wide model with one
 collective per row-parallel linear, NCCL and fused.
